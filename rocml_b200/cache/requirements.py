@@ -13,13 +13,20 @@ class KVRequirement:
     ``shared_values``: one tensor serves as both (a layer that caches a single vector a token, from
     which it derives keys and values); ``view.v`` is then ``view.k``.  ``chunk``: a query reads only
     the keys of its own block of that many positions (blocks counted from position 0), so the pages
-    of earlier blocks come back as the sequence grows."""
+    of earlier blocks come back as the sequence grows.  ``keep_first``: beside its window a query
+    reads the keys at positions below this, so the pages that hold any of them are never given back."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     shared_values: bool = False
     chunk: Optional[int] = None
+    keep_first: int = 0
+
+    @property
+    def kept_pages(self) -> int:
+        """How many pages at the start of a sequence a window never releases (pages of 64 tokens)."""
+        return (self.keep_first + 63) // 64 if self.releases else 0
 
     def first_needed(self, length: int) -> int:
         """The lowest position that a query at position >= ``length`` can still read (0: everything stays)."""

@@ -69,8 +69,10 @@ class KVGroup:
         if need > self.max_pages_per_seq:
             raise ContextOverflow(new_len, self.max_pages_per_seq * PAGE)
         row = self.table_host[slot]
-        first = max(self._released_upto.get(slot, 0), pages_for(old_len)) if old_len else self._released_upto.get(slot, 0)
-        todo = [p for p in range(first, need) if row[p] < 0]
+        # the pages a window has given back are [kept, upto): those before them hold positions that stay visible
+        kept, upto = self.req.kept_pages, self._released_upto.get(slot, 0)
+        first = pages_for(old_len) if old_len else 0
+        todo = [p for p in range(first, need) if row[p] < 0 and not kept <= p < upto]
         if len(todo) > self.pool.n_free:
             raise CacheFull(
                 f"the cache has {self.pool.n_free} free pages of {PAGE} tokens, {len(todo)} are needed "
@@ -89,14 +91,16 @@ class KVGroup:
         for n_piece, piece in enumerate(pieces):
             for slot, n_new in piece:
                 if slot not in state:
-                    # a sequence holds the pages of its length so far, from the first its window has not released
-                    state[slot] = [self._released_upto.get(slot, 0), pages_for(lengths[slot]), lengths[slot]]
+                    # a sequence holds the pages of its length so far, but for those its window has released:
+                    # [kept, st[0]), where kept pages at the start are never released
+                    state[slot] = [max(self._released_upto.get(slot, 0), self.req.kept_pages), pages_for(lengths[slot]),
+                                   lengths[slot]]
                 st = state[slot]
                 st[2] += n_new
                 need = pages_for(st[2])
                 if need > self.max_pages_per_seq:
                     raise ContextOverflow(st[2], self.max_pages_per_seq * PAGE)
-                todo = max(0, need - max(st[0], st[1]))
+                todo = max(0, need - st[1])
                 if todo > free:
                     raise CacheFull(
                         f"the cache has {free} free pages of {PAGE} tokens when piece {n_piece} of the step "
@@ -108,9 +112,9 @@ class KVGroup:
                 continue
             for slot, _ in piece:
                 st = state[slot]
-                keep_from = self.req.first_needed(st[2]) // PAGE
+                keep_from = min(self.req.first_needed(st[2]) // PAGE, st[1])
                 if keep_from > st[0]:
-                    free += max(0, min(keep_from, st[1]) - st[0])
+                    free += keep_from - st[0]
                     st[0] = keep_from
 
     def release_out_of_window(self, slot: int, length: int) -> None:
@@ -121,7 +125,7 @@ class KVGroup:
             return
         keep_from = self.req.first_needed(length) // PAGE
         row = self.table_host[slot]
-        start = self._released_upto.get(slot, 0)
+        start = max(self._released_upto.get(slot, 0), self.req.kept_pages)
         for p in range(start, keep_from):
             if row[p] >= 0:
                 self.pool.free(int(row[p]))
@@ -256,7 +260,7 @@ class SequenceCache:
         for req, members in kv_members.items():
             n_pages = self.n_pages
             if req.releases and max_step_tokens:
-                per_seq = pages_for(req.span + max_step_tokens) + 1
+                per_seq = pages_for(req.span + max_step_tokens) + 1 + req.kept_pages
                 n_pages = min(n_pages, max_slots * per_seq)
             g = KVGroup(req, len(members), n_pages, max_slots, self.max_pages_per_seq, dtype, device)
             self.kv_groups.append(g)

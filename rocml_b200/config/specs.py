@@ -33,10 +33,12 @@ def tensor_names(params: Mapping[str, Any], defaults: Mapping[str, str]) -> dict
 
 @dataclass(frozen=True)
 class NormSpec:
-    """A normalisation over the last axis.  kind "rmsnorm": x * rsqrt(mean(x^2) + eps) * w."""
+    """A normalisation over the last axis.  kind "rmsnorm": x * rsqrt(mean(x^2) + eps) * (w + weight_offset);
+    ``weight_offset`` 1 is a weight that the files store around zero."""
 
     kind: str = "rmsnorm"
     eps: float = 1e-6
+    weight_offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -46,7 +48,9 @@ class PositionSpec:
     kind "rope_neox": rotate-half rotary embedding over the first ``rot_dim``
     dimensions of every head with base ``theta``; kind "rope_pairs": the same with
     neighbouring entries (2i, 2i + 1) as pairs; both take the parameter ``scaling``
-    ({factor, low, high, original}: long wavelengths stretched); kind "none": nothing.
+    ({factor, low, high, original}: long wavelengths stretched) or ``ramp_scaling``
+    ({factor, original, fast, slow}: frequencies blended between f and f / factor along a ramp over
+    the pair index, and cosines and sines times 0.1 ln(factor) + 1); kind "none": nothing.
     As a model's ``input_position`` (added to the embedding output, not applied inside a mixer):
     kind "sinusoid": entry 2i of the vector is sin(pos * theta^(-2i / width)), entry 2i + 1 the cosine.
     """
@@ -74,7 +78,15 @@ class MixerSpec:
     q_norm, k_norm, gate_proj), v_head_dim (the value heads' size when it is not
     head_dim), chunk (a query sees the earlier keys of its own block of that many
     positions, blocks counted from position 0; not together with window), gated (head
-    n's result is multiplied by sigmoid(Wgate x)_n before the output projection).
+    n's result is multiplied by sigmoid(Wgate x)_n before the output projection; "per_value": the
+    gate has a number for every value of every head), bias as a list of the roles that have
+    one (["q", "k", "v"]) instead of all or none, keep_first (with a window: the keys at positions
+    below it stay visible to every later query), sink (a score s: every row's softmax denominator
+    has one more term exp(s) that brings no value), qk_unit_norm (queries and keys divided by their
+    root mean square over the head, without a weight, after the position encoding; eps is
+    qk_norm_eps), value_mix ("source": this layer's values as projected are kept for the step;
+    "mix": what is cached and read is (1 - lambda) v + lambda v_source, lambda the layer's scalar
+    tensor of role value_mix, v_source the values of the same token in the step's source layer).
     """
 
     kind: str
@@ -129,6 +141,8 @@ class LayerSpec:
     """One layer: two norms, a mixer and a feed-forward in a named arrangement.
 
     arrangement "pre_norm": x += mixer(norm1(x)); x += ff(norm2(x)).
+    arrangement "parallel": x += mixer(norm1(x)) + ff(norm1(x)); "parallel_two_norms": x += mixer(norm1(x)) +
+    ff(norm2(x)), both norms of the same x.
     arrangement "sandwich_norm": x += post1(mixer(norm1(x))); x += post2(ff(norm2(x))), with the two
     post norms given by ``mixer_post_norm`` and ``ff_post_norm``; ``feed_forward`` None leaves the second half out.
     ``prefix`` is the layer's tensor-name prefix in the weight files; under it the four parts'
@@ -193,6 +207,9 @@ class ModelSpec:
     input_position: Optional[PositionSpec] = None      # a position vector added to the embedding output
     logit_scale: float = 1.0                           # the head's result is multiplied by it
     weight_suffix: str = ".weight"                     # what the files append to a part's tensor-name stem
+    bias_suffix: str = ".bias"                         # the same for a part's '<stem>.bias'
+    embedding_norm: Optional[NormSpec] = None          # a norm of the embedding output, before the first layer
+    embedding_norm_name: str = "model.embed_norm.weight"
 
     def __post_init__(self):
         n = len(self.layers)

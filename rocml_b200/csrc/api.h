@@ -11,7 +11,7 @@ int rb_embedding(const int* ids, const void* table, int table_dtype, float* out,
 
 int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, long long delta_stride, const void* w,
                    int w_dtype, void* out, int out_dtype, const int* rows, int n_rows, int H, float eps,
-                   int write_back, void* stream);
+                   int write_back, const void* w2, void* out2, void* stream);
 
 int rb_silu_mul(const void* in, int in_dtype, int n_in, long long in_stride, void* out, int out_dtype, int rows,
                 int I, int paired, void* stream);
@@ -40,8 +40,11 @@ int rb_gated_act(const void* in, int in_dtype, int n_in, long long in_stride, lo
 
 int rb_scale(float* x, long long n, float factor, void* stream);
 
-// out[t, h, :out_w] = in[t, h, :out_w] * gate[t, h] for heads of in_w (>= out_w) values; gate float32 or absent.
+// out[t, h, :out_w] = in[t, h, :out_w] * gate for heads of in_w (>= out_w) values; gate float32 [T, heads * gate_w]
+// (gate_w 1: one a head, out_w: one a value), or the sigmoid of `raw` (such columns of projection rows, n_in
+// partial sums), or absent.
 int rb_head_gate(const void* in, long long ld_in, int in_w, void* out, long long ld_out, int out_w, const float* gate,
+                 int gate_w, const void* raw, int raw_dtype, int n_in, long long in_stride, long long row_stride,
                  int heads, int T, int dtype, void* stream);
 
 // A latent-attention layer's projection rows [queries | latent | gate logits]: latent normalised into the paged
@@ -106,9 +109,10 @@ int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, long long in_s
                           const void* k_norm_w, int w_dtype, float eps, const float* inv_freq, int rot_dim,
                           const int* positions, const int* slot_of_token, const int* block_table, int max_pages,
                           void* k_cache, void* v_cache, int write_kv, const void* cos_sin, int vd, int hdp,
-                          int interleaved, int n_gate, float* gate_out, void* stream);
+                          int interleaved, int n_gate, float* gate_out, int post_norm, const float* v_first,
+                          const float* v_lambda, float* v_out, void* stream);
 
-int rb_rope_table(const int* positions, const float* inv_freq, int T, int half, void* out, void* stream);
+int rb_rope_table(const int* positions, const float* inv_freq, int T, int half, float mag, void* out, void* stream);
 
 int rb_gemm_generic(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias, void* out,
                     int out_dtype, int M, int N, int K, long long ldx, long long ldo, int splits,
@@ -149,8 +153,8 @@ int rb_gemm_tcgen05_add(const void* x, const void* w, const float* bias, float* 
 int rb_attention_generic(const void* q, int q_stride, void* out, int o_stride, int dtype, const void* k_cache,
                          const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
                          const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv, int hd,
-                         float scale, int window, int chunk, int n_chunks, float* part_acc, float* part_ml,
-                         void* stream);
+                         float scale, int window, int keep, float sink, int chunk, int n_chunks, float* part_acc,
+                         float* part_ml, void* stream);
 
 int rb_attention_prefill(const void* q, int q_stride, void* out, int o_stride, const void* k_cache,
                          const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
@@ -178,7 +182,7 @@ int rb_attention_decode_fused(const float* proj, int n_in, long long in_stride, 
 
 int rb_attention_merge(const float* part_acc, const float* part_ml, void* out, int o_stride, int dtype,
                        const int* positions, const int* slot_of_token, int T, int nq, int hd, int chunk,
-                       int n_chunks, int window, void* stream);
+                       int n_chunks, int window, int keep, float sink, void* stream);
 
 int rb_argmax(const float* logits, long long row_stride, int rows, int V, int* out, float* scratch_v,
               int* scratch_i, int slices, void* stream);

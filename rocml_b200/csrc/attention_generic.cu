@@ -47,7 +47,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ block_table, int max_pages,
                          const int* __restrict__ seq_slot, const int* __restrict__ cu_q,
                          const int* __restrict__ kv_len, int nq, int nkv, int hd, float scale, int window,
-                         int chunk, int n_chunks, float* __restrict__ part_acc,
+                         int keep, float sink, int chunk, int n_chunks, float* __restrict__ part_acc,
                          float* __restrict__ part_ml) {
     pdl_trigger();
     pdl_wait();
@@ -138,10 +138,12 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         if (!prefix) n_rows = RW;
     }
 
-    // key range of the whole block, then of this chunk
+    // key range of the whole block, then of this chunk: the keys [lo, hi] of which those in [keep, blo) are
+    // hidden from every row of the block (blo: where the window of the block's first query starts)
     const int last_tok = min(tok0 + QB, q_len) - 1;
     int hi = pos0 + last_tok;                                       // inclusive
-    int lo = span_lo(pos0 + tok0, window);
+    const int blo = span_lo(pos0 + tok0, window);
+    int lo = keep > 0 ? 0 : blo;
     if (chunk > 0) {
         lo = max(lo, c * chunk);
         hi = min(hi, (c + 1) * chunk - 1);
@@ -152,8 +154,10 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     const bool vec = (hd & 3) == 0 && (((uintptr_t)k_cache | (uintptr_t)v_cache) & (4 * sizeof(T) - 1)) == 0 &&
                      ((ROWS * hd + KT * (hd + 1)) & 3) == 0;
 
+    __syncthreads();      // q_s written
     for (int t0 = (lo / KT) * KT; t0 <= hi; t0 += KT) {
-        __syncthreads();  // previous tile fully consumed (and q_s written, first time)
+        if (t0 >= keep && t0 + KT <= blo) { t0 = (blo / KT) * KT - KT; continue; }   // a tile between the kept keys and the window
+        __syncthreads();  // previous tile fully consumed
         const int page = table[t0 / RB_PAGE];
         const size_t base = page >= 0 ? (((size_t)page * nkv + kvh) * RB_PAGE + (t0 % RB_PAGE)) * hd : 0;
         if (vec) {
@@ -166,7 +170,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 #pragma unroll
                 for (int u = 0; u < KPW; ++u) {
                     const int jj = warp + 4 * u;
-                    const bool in = page >= 0 && t0 + jj <= hi && t0 + jj >= lo;
+                    const bool in = page >= 0 && t0 + jj <= hi && t0 + jj >= lo && (t0 + jj >= blo || t0 + jj < keep);
                     const size_t off = base + (size_t)jj * hd + d4 * 4;
                     kk[u] = in ? load4(k_cache + off) : make_float4(0.f, 0.f, 0.f, 0.f);
                     vv[u] = in ? load4(v_cache + off) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -182,7 +186,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         } else {
             for (int idx = tid; idx < KT * hd; idx += blockDim.x) {
                 const int jj = idx / hd, d = idx - jj * hd;
-                const bool in = page >= 0 && t0 + jj <= hi && t0 + jj >= lo;
+                const bool in = page >= 0 && t0 + jj <= hi && t0 + jj >= lo && (t0 + jj >= blo || t0 + jj < keep);
                 k_s[jj * (hd + 1) + d] = in ? to_f32(k_cache[base + idx]) : 0.f;
                 v_s[idx] = in ? to_f32(v_cache[base + idx]) : 0.f;
             }
@@ -204,7 +208,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
             float p[NR];
 #pragma unroll
             for (int i = 0; i < NR; ++i) {
-                const bool valid = row_ok[i] && j <= row_pos[i] && j >= row_lo[i] && j <= hi && j >= lo;
+                const bool valid = row_ok[i] && j <= row_pos[i] && (j >= row_lo[i] || j < keep) && j <= hi && j >= lo;
                 const float sv = s[i] * scale;
                 const float tmax = warp_max(valid ? sv : NEG_BIG);
                 const float m_new = fmaxf(m[i], tmax);
@@ -251,7 +255,9 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 if (d < hd) part_acc[pidx * hd + d] = acc[i][dd];
             }
         } else {
-            const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+            float lsum = l[i];
+            const float a = has_sink(sink) ? add_sink(m[i], lsum, sink) : 1.f;
+            const float inv = lsum > 0.f ? a / lsum : 0.f;
 #pragma unroll
             for (int dd = 0; dd < DPL; ++dd) {
                 const int d = lane + 32 * dd;
@@ -268,7 +274,7 @@ template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                        T* __restrict__ out, int o_stride, const int* __restrict__ positions,
                                        const int* __restrict__ slot_of_token, int T_tokens, int nq, int hd,
-                                       int chunk, int n_chunks, int window) {
+                                       int chunk, int n_chunks, int window, int keep, float sink) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float w_s[];   // [warps][n_chunks]
@@ -280,29 +286,35 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
     if (slot_of_token[t] < 0) return;
     const int pos = positions[t];
     const int c_hi = min(n_chunks - 1, pos / chunk);
-    const int c_lo = span_lo(pos, window) / chunk;
+    // the chunks that hold keys this row sees: those of its window, and those of the kept first keys
+    const int c_win = span_lo(pos, window) / chunk;
+    const int c_kept = keep > 0 ? (min(keep, pos + 1) - 1) / chunk : -1;     // the last chunk with a kept key
+    const int c_lo = keep > 0 ? 0 : c_win;
     const size_t base = ((size_t)t * nq + head) * n_chunks;
     float* w = w_s + (size_t)warp * n_chunks;
     float M = NEG_BIG;
     for (int c = c_lo + lane; c <= c_hi; c += 32)
-        if (part_ml[(base + c) * 2 + 1] > 0.f) M = fmaxf(M, part_ml[(base + c) * 2]);
+        if ((c >= c_win || c <= c_kept) && part_ml[(base + c) * 2 + 1] > 0.f) M = fmaxf(M, part_ml[(base + c) * 2]);
     M = warp_max(M);
     float L = 0.f;
     for (int c = c_lo + lane; c <= c_hi; c += 32) {
-        const float lc = part_ml[(base + c) * 2 + 1];
+        const bool used = c >= c_win || c <= c_kept;
+        const float lc = used ? part_ml[(base + c) * 2 + 1] : 0.f;
         const float wc = lc > 0.f ? expf(part_ml[(base + c) * 2] - M) : 0.f;
         w[c] = wc;
         L += wc * lc;
     }
     L = warp_sum(L);
     __syncwarp();
-    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const float a_sink = has_sink(sink) ? add_sink(M, L, sink) : 1.f;
+    const float inv = L > 0.f ? a_sink / L : 0.f;
     for (int d = lane; d < hd; d += 32) {
         float a = 0.f;
         for (int c0 = c_lo; c0 <= c_hi; c0 += 8) {        // eight chunks' values in flight, added in ascending order
             float pa[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) pa[j] = c0 + j <= c_hi ? part_acc[(base + c0 + j) * hd + d] : 0.f;
+            for (int j = 0; j < 8; ++j)
+                pa[j] = c0 + j <= c_hi && (c0 + j >= c_win || c0 + j <= c_kept) ? part_acc[(base + c0 + j) * hd + d] : 0.f;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
                 if (c0 + j <= c_hi) a = fmaf(w[c0 + j], pa[j], a);
@@ -315,7 +327,7 @@ template <typename T>
 int launch_attn(const void* q, int q_stride, void* out, int o_stride, const void* k_cache, const void* v_cache,
                 const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                 const int* kv_len, int B, int max_q_len, int nq, int nkv, int hd, float scale, int window,
-                int chunk, int n_chunks, float* part_acc, float* part_ml, cudaStream_t s) {
+                int keep, float sink, int chunk, int n_chunks, float* part_acc, float* part_ml, cudaStream_t s) {
     const int g = nq / nkv;
     const int HG = g < ROWS ? g : ROWS;
     const int QB = ROWS / HG;
@@ -331,7 +343,7 @@ int launch_attn(const void* q, int q_stride, void* out, int o_stride, const void
     dim3 grid((unsigned)gx, nkv * head_chunks, B);
     RB_LAUNCH((k), dim3(grid), dim3(128), smem, s, (const T*)q, q_stride, (T*)out, o_stride, (const T*)k_cache, (const T*)v_cache,
                               block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, hd, scale, window,
-                              chunk, n_chunks, part_acc, part_ml);
+                              keep, sink, chunk, n_chunks, part_acc, part_ml);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }
@@ -341,8 +353,10 @@ extern "C" int rb_attention_generic(const void* q, int q_stride, void* out, int 
                                     const void* k_cache, const void* v_cache, const int* block_table,
                                     int max_pages, const int* seq_slot, const int* cu_q, const int* kv_len,
                                     int B, int max_q_len, int nq, int nkv, int hd, float scale, int window,
-                                    int chunk, int n_chunks, float* part_acc, float* part_ml, void* stream) {
+                                    int keep, float sink, int chunk, int n_chunks, float* part_acc, float* part_ml,
+                                    void* stream) {
     if (B <= 0 || max_q_len <= 0) return RB_OK;
+    if (keep < 0 || (keep > 0 && window < 0)) return RB_ERR_BAD_SIZE;
     if (hd <= 0 || hd > 32 * MAX_DPL || nkv <= 0 || nq % nkv) return RB_ERR_BAD_SIZE;
     if (chunk > 0 && (chunk % KT || n_chunks <= 0 || !part_acc || !part_ml)) return RB_ERR_BAD_SIZE;
     if (chunk <= 0) n_chunks = 1;
@@ -350,17 +364,17 @@ extern "C" int rb_attention_generic(const void* q, int q_stride, void* out, int 
     if (dtype == RB_BF16)
         return launch_attn<__nv_bfloat16>(q, q_stride, out, o_stride, k_cache, v_cache, block_table, max_pages,
                                           seq_slot, cu_q, kv_len, B, max_q_len, nq, nkv, hd, scale, window,
-                                          chunk, n_chunks, part_acc, part_ml, s);
+                                          keep, sink, chunk, n_chunks, part_acc, part_ml, s);
     if (dtype == RB_F32)
         return launch_attn<float>(q, q_stride, out, o_stride, k_cache, v_cache, block_table, max_pages, seq_slot,
-                                  cu_q, kv_len, B, max_q_len, nq, nkv, hd, scale, window, chunk, n_chunks,
+                                  cu_q, kv_len, B, max_q_len, nq, nkv, hd, scale, window, keep, sink, chunk, n_chunks,
                                   part_acc, part_ml, s);
     return RB_ERR_BAD_DTYPE;
 }
 
 extern "C" int rb_attention_merge(const float* part_acc, const float* part_ml, void* out, int o_stride,
                                   int dtype, const int* positions, const int* slot_of_token, int T, int nq,
-                                  int hd, int chunk, int n_chunks, int window, void* stream) {
+                                  int hd, int chunk, int n_chunks, int window, int keep, float sink, void* stream) {
     if (T <= 0) return RB_OK;
     if (chunk <= 0 || n_chunks <= 0) return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
@@ -372,11 +386,11 @@ extern "C" int rb_attention_merge(const float* part_acc, const float* part_ml, v
     if (dtype == RB_BF16)
         RB_LAUNCH((attention_merge_kernel<__nv_bfloat16>), dim3((int)blocks), dim3(warps * 32), smem, s, part_acc, part_ml, (__nv_bfloat16*)out, o_stride,
                                                                   positions, slot_of_token, T, nq, hd, chunk,
-                                                                  n_chunks, window);
+                                                                  n_chunks, window, keep, sink);
     else if (dtype == RB_F32)
         RB_LAUNCH((attention_merge_kernel<float>), dim3((int)blocks), dim3(warps * 32), smem, s, part_acc, part_ml, (float*)out, o_stride,
                                                                   positions, slot_of_token, T, nq, hd, chunk,
-                                                                  n_chunks, window);
+                                                                  n_chunks, window, keep, sink);
     else
         return RB_ERR_BAD_DTYPE;
     RB_LAUNCH_CHECK();

@@ -89,6 +89,21 @@ __device__ __forceinline__ int span_lo(int pos, int window) {
     return window > 0 ? max(0, pos - window + 1) : (window < 0 ? pos - pos % (-window) : 0);
 }
 
+// Two more parts of a layer's mask and weights, beside `window`.  `keep` (>= 0): the keys at positions below it
+// stay visible to every later query whatever the window says (they keep their own positions).  `sink`: one more
+// term exp(sink) in the softmax's denominator, with no value of its own (RB_NO_SINK: none); a row's weights then
+// sum to less than one.
+#define RB_NO_SINK (-3.0e38f)
+__device__ __forceinline__ bool has_sink(float sink) { return sink > -1.0e38f; }
+// What the sink does to a finished row: with running maximum m and sum l, the factor for the accumulated values
+// (returned) and the new sum (through l): m' = max(m, sink), l' = l e^(m - m') + e^(sink - m').
+__device__ __forceinline__ float add_sink(float m, float& l, float sink) {
+    const float m2 = fmaxf(m, sink);
+    const float a = expf(m - m2);
+    l = l * a + expf(sink - m2);
+    return a;
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

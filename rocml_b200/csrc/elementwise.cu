@@ -71,7 +71,8 @@ extern "C" int rb_embedding(const int* ids, const void* table, int table_dtype, 
 // ---- fused residual add + RMSNorm ---------------------------------------------------------
 // r = resid[row] + sum_s delta[s][row]   (s in fixed order, so the sum never depends on the batch)
 // if write_back: resid[row] = r
-// out[i] = r * rsqrt(mean(r^2) + eps) * w
+// out[i] = r * rsqrt(mean(r^2) + eps) * w      (and out2[i] = the same row times w2, when a second weight is given:
+//                                               two norms of one row that differ in their weights only)
 // `rows` (optional) picks the source rows; output row i is compact.  One block per output row.
 // Replaces add_inplace_f32 + rmsnorm_f32 (rocml-kernels/kernels/elementwise.hip:7-26,
 // rmsnorm.hip:7-43); product order x * inv_rms * w as there.
@@ -97,7 +98,7 @@ template <typename OT, typename WT>
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ delta,
                                    int n_delta, size_t delta_stride, const WT* __restrict__ w,
                                    OT* __restrict__ out, const int* __restrict__ rows, int H,
-                                   float eps, int write_back) {
+                                   float eps, int write_back, const WT* __restrict__ w2, OT* __restrict__ out2) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float row_buf[];  // H floats (padded to 4) + 33 for the reduction
@@ -150,12 +151,17 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ r
             if (write_back) r4[i] = v;
             store4(o + 4 * i, v.x * inv * to_f32(w[4 * i]), v.y * inv * to_f32(w[4 * i + 1]),
                    v.z * inv * to_f32(w[4 * i + 2]), v.w * inv * to_f32(w[4 * i + 3]), out_vec);
+            if (out2)
+                store4(out2 + (size_t)orow * H + 4 * i, v.x * inv * to_f32(w2[4 * i]), v.y * inv * to_f32(w2[4 * i + 1]),
+                       v.z * inv * to_f32(w2[4 * i + 2]), v.w * inv * to_f32(w2[4 * i + 3]),
+                       out_vec && ((uintptr_t)out2 & 15) == 0);
         }
     } else {
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
             const float v = row_buf[i];
             if (write_back) r[i] = v;
             o[i] = from_f32<OT>(v * inv * to_f32(w[i]));
+            if (out2) out2[(size_t)orow * H + i] = from_f32<OT>(v * inv * to_f32(w2[i]));
         }
     }
 }
@@ -169,7 +175,8 @@ __global__ void __launch_bounds__(THREADS) add_rmsnorm_rows_kernel(float* __rest
                                                                    int n_delta, size_t delta_stride,
                                                                    const WT* __restrict__ w, OT* __restrict__ out,
                                                                    const int* __restrict__ rows, int H, float eps,
-                                                                   int write_back) {
+                                                                   int write_back, const WT* __restrict__ w2,
+                                                                   OT* __restrict__ out2) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[33];
@@ -212,6 +219,9 @@ __global__ void __launch_bounds__(THREADS) add_rmsnorm_rows_kernel(float* __rest
             if (write_back) r4[i] = v[j];
             store4(o + 4 * i, v[j].x * inv * to_f32(w[4 * i]), v[j].y * inv * to_f32(w[4 * i + 1]),
                    v[j].z * inv * to_f32(w[4 * i + 2]), v[j].w * inv * to_f32(w[4 * i + 3]), true);
+            if (out2)
+                store4(out2 + (size_t)orow * H + 4 * i, v[j].x * inv * to_f32(w2[4 * i]), v[j].y * inv * to_f32(w2[4 * i + 1]),
+                       v[j].z * inv * to_f32(w2[4 * i + 2]), v[j].w * inv * to_f32(w2[4 * i + 3]), true);
         }
     }
 }
@@ -219,19 +229,20 @@ __global__ void __launch_bounds__(THREADS) add_rmsnorm_rows_kernel(float* __rest
 template <typename OT, typename WT>
 static int launch_add_rmsnorm(float* resid, const float* delta, int n_delta, size_t delta_stride,
                               const void* w, void* out, const int* rows, int n_rows, int H, float eps,
-                              int write_back, cudaStream_t s) {
+                              int write_back, const void* w2, void* out2, cudaStream_t s) {
     // many rows: the register kernel, when everything is 16-byte aligned and a row fits its threads
     // (up to 256 rows are at most one wave of the kernel below, whose 1,024 threads a row finish sooner)
     const bool aligned = (H & 3) == 0 && (delta_stride & 3) == 0 &&
                          ((((uintptr_t)resid | (uintptr_t)delta) & 15) == 0) &&
-                         ((((uintptr_t)out | ((size_t)H * sizeof(OT))) & 15) == 0) && (((uintptr_t)w & (4 * sizeof(WT) - 1)) == 0);
+                         ((((uintptr_t)out | (uintptr_t)out2 | ((size_t)H * sizeof(OT))) & 15) == 0) &&
+                         ((((uintptr_t)w | (uintptr_t)w2) & (4 * sizeof(WT) - 1)) == 0);
     if (n_rows > (H >= 4096 ? 256 : 64) && aligned && H <= 8 * 4 * 256) {
         if (H <= 8 * 4 * 128)
             RB_LAUNCH((add_rmsnorm_rows_kernel<OT, WT, 128>), dim3(n_rows), dim3(128), 0, s, resid, delta, n_delta,
-                      delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back);
+                      delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back, (const WT*)w2, (OT*)out2);
         else
             RB_LAUNCH((add_rmsnorm_rows_kernel<OT, WT, 256>), dim3(n_rows), dim3(256), 0, s, resid, delta, n_delta,
-                      delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back);
+                      delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back, (const WT*)w2, (OT*)out2);
         RB_LAUNCH_CHECK();
         return RB_OK;
     }
@@ -245,25 +256,26 @@ static int launch_add_rmsnorm(float* resid, const float* delta, int n_delta, siz
     // one 16-byte column group per thread where the row allows it: a row's loads are all in flight at once
     const int threads = H >= 4096 ? 1024 : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
     RB_LAUNCH((k), dim3(n_rows), dim3(threads), smem, s, resid, delta, n_delta, delta_stride, (const WT*)w, (OT*)out, rows, H,
-                                    eps, write_back);
+                                    eps, write_back, (const WT*)w2, (OT*)out2);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }
 
 extern "C" int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, long long delta_stride,
                               const void* w, int w_dtype, void* out, int out_dtype, const int* rows,
-                              int n_rows, int H, float eps, int write_back, void* stream) {
+                              int n_rows, int H, float eps, int write_back, const void* w2, void* out2, void* stream) {
     if (n_rows <= 0) return RB_OK;
+    if ((w2 == nullptr) != (out2 == nullptr)) return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t ds = (size_t)delta_stride;
     if (out_dtype == RB_BF16 && w_dtype == RB_BF16)
-        return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, s);
+        return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, s);
     if (out_dtype == RB_BF16 && w_dtype == RB_F32)
-        return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, s);
+        return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, s);
     if (out_dtype == RB_F32 && w_dtype == RB_BF16)
-        return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, s);
+        return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, s);
     if (out_dtype == RB_F32 && w_dtype == RB_F32)
-        return launch_add_rmsnorm<float, float>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, s);
+        return launch_add_rmsnorm<float, float>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, s);
     return RB_ERR_BAD_DTYPE;
 }
 
@@ -610,16 +622,22 @@ extern "C" int rb_gated_act(const void* in, int in_dtype, int n_in, long long in
     return RB_OK;
 }
 
-// ---- heads of an attention result times a gate a head, narrowed to the values' width ------------------------
-// in [T, heads, in_w] -> out [T, heads, out_w] (out_w <= in_w: what lies beyond is padding), each head of a token
-// multiplied by gate[t, head] (float32; absent: 1).  The product is formed in 32-bit.
-template <typename AT>
+// ---- heads of an attention result times a gate, narrowed to the values' width ----------------------------------
+// in [T, heads, in_w] -> out [T, heads, out_w] (out_w <= in_w: what lies beyond is padding), multiplied by a gate
+// formed in 32-bit.  The gate is either finished, float32 [T, heads * gate_w] (gate_w 1: one a head; gate_w = out_w:
+// one a value), or `raw`: columns of the projection rows (n_in partial sums added first, in order), of which the
+// kernel takes the sigmoid itself.  Absent: 1.
+template <typename AT, typename RT>
 __global__ void head_gate_kernel(const AT* __restrict__ in, long long ld_in, int in_w, AT* __restrict__ out, long long ld_out,
-                                 int out_w, const float* __restrict__ gate, int heads, int T) {
+                                 int out_w, const float* __restrict__ gate, int gate_w, const RT* __restrict__ raw, int n_in,
+                                 long long in_stride, long long row_stride, int heads, int T) {
     pdl_trigger();
     pdl_wait();
+    const bool each = gate_w > 1;
     if ((in_w & 3) == 0 && (out_w & 3) == 0 && (ld_in & 3) == 0 && (ld_out & 3) == 0 &&
-        (((uintptr_t)in | (uintptr_t)out) & (4 * sizeof(AT) - 1)) == 0) {
+        (((uintptr_t)in | (uintptr_t)out) & (4 * sizeof(AT) - 1)) == 0 &&
+        (!raw || !each || ((row_stride & 3) == 0 && (in_stride & 3) == 0 && ((uintptr_t)raw & (4 * sizeof(RT) - 1)) == 0)) &&
+        (!gate || !each || ((uintptr_t)gate & 15) == 0)) {
         // four neighbouring values a thread
         const int w4 = out_w >> 2;
         const size_t n4 = (size_t)T * heads * w4;
@@ -628,10 +646,28 @@ __global__ void head_gate_kernel(const AT* __restrict__ in, long long ld_in, int
             const int d = (int)(idx - th * w4) * 4;
             const size_t t = th / heads;
             const int h = (int)(th - t * heads);
-            const float g = gate ? gate[th] : 1.f;
+            float g[4] = {1.f, 1.f, 1.f, 1.f};
+            if (raw && each) {
+                float z[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int s = 0; s < n_in; ++s) {
+                    float r[4];
+                    load4(raw + (size_t)s * in_stride + t * row_stride + (size_t)h * out_w + d, r);
+                    z[0] += r[0]; z[1] += r[1]; z[2] += r[2]; z[3] += r[3];
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) g[j] = 1.f / (1.f + expf(-z[j]));
+            } else if (raw) {
+                float z = 0.f;
+                for (int s = 0; s < n_in; ++s) z += to_f32(raw[(size_t)s * in_stride + t * row_stride + h]);
+                g[0] = g[1] = g[2] = g[3] = 1.f / (1.f + expf(-z));
+            } else if (gate && each) {
+                load4(gate + th * out_w + d, g);
+            } else if (gate) {
+                g[0] = g[1] = g[2] = g[3] = gate[th];
+            }
             float x[4];
             load4(in + t * ld_in + (size_t)h * in_w + d, x);
-            x[0] *= g; x[1] *= g; x[2] *= g; x[3] *= g;
+            x[0] *= g[0]; x[1] *= g[1]; x[2] *= g[2]; x[3] *= g[3];
             store4(out + t * ld_out + (size_t)h * out_w + d, x);
         }
         return;
@@ -642,28 +678,38 @@ __global__ void head_gate_kernel(const AT* __restrict__ in, long long ld_in, int
         const int d = (int)(idx - th * out_w);
         const size_t t = th / heads;
         const int h = (int)(th - t * heads);
-        const float g = gate ? gate[th] : 1.f;
+        float g = 1.f;
+        if (raw) {
+            float z = 0.f;
+            const size_t col = each ? (size_t)h * out_w + d : (size_t)h;
+            for (int s = 0; s < n_in; ++s) z += to_f32(raw[(size_t)s * in_stride + t * row_stride + col]);
+            g = 1.f / (1.f + expf(-z));
+        } else if (gate) {
+            g = each ? gate[th * out_w + d] : gate[th];
+        }
         out[t * ld_out + (size_t)h * out_w + d] = from_f32<AT>(to_f32(in[t * ld_in + (size_t)h * in_w + d]) * g);
     }
 }
 
 extern "C" int rb_head_gate(const void* in, long long ld_in, int in_w, void* out, long long ld_out, int out_w,
-                            const float* gate, int heads, int T, int dtype, void* stream) {
+                            const float* gate, int gate_w, const void* raw, int raw_dtype, int n_in, long long in_stride,
+                            long long row_stride, int heads, int T, int dtype, void* stream) {
     if (T <= 0 || heads <= 0) return RB_OK;
-    if (out_w <= 0 || out_w > in_w) return RB_ERR_BAD_SIZE;
+    if (out_w <= 0 || out_w > in_w || (gate_w != 1 && gate_w != out_w) || (raw && (gate || n_in < 1))) return RB_ERR_BAD_SIZE;
     const size_t n = (size_t)T * heads * out_w;
     const int threads = 256;
     const size_t want = (n + threads - 1) / threads;
     const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == RB_BF16)
-        RB_LAUNCH((head_gate_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)in, ld_in, in_w,
-                  (__nv_bfloat16*)out, ld_out, out_w, gate, heads, T);
-    else if (dtype == RB_F32)
-        RB_LAUNCH((head_gate_kernel<float>), dim3(blocks), dim3(threads), 0, s, (const float*)in, ld_in, in_w, (float*)out,
-                  ld_out, out_w, gate, heads, T);
-    else
-        return RB_ERR_BAD_DTYPE;
+    typedef __nv_bfloat16 bf;
+#define RB_HG(AT, RT)                                                                                                   \
+    RB_LAUNCH((head_gate_kernel<AT, RT>), dim3(blocks), dim3(threads), 0, s, (const AT*)in, ld_in, in_w, (AT*)out, ld_out, \
+              out_w, gate, gate_w, (const RT*)raw, n_in, in_stride, row_stride, heads, T)
+    if (dtype == RB_BF16 && (!raw || raw_dtype == RB_BF16)) RB_HG(bf, bf);
+    else if (dtype == RB_BF16 && raw_dtype == RB_F32) RB_HG(bf, float);
+    else if (dtype == RB_F32 && (!raw || raw_dtype == RB_F32)) RB_HG(float, float);
+    else return RB_ERR_BAD_DTYPE;
+#undef RB_HG
     RB_LAUNCH_CHECK();
     return RB_OK;
 }

@@ -15,7 +15,12 @@
 // The general kernel also takes value heads of another width than the key heads (`vd`), writes every
 // head `hdp` wide (zeros beyond its own width: queries and keys padded with zeros score the same, and
 // padded values give zeros that the consumer drops), so that one attention kernel with one head size
-// serves them, and turns `n_gate` more columns of the row into sigmoid gates (32-bit).
+// serves them, and turns `n_gate` more columns of the row into sigmoid gates (32-bit).  Further options of the
+// general kernel: `post_norm`, queries and keys divided by their root mean square over the head after the rotation
+// (no weight); `v_out`, the value heads as they came from the projection, 32-bit [T, nkv * vd], for later layers;
+// `v_first` and `v_lambda`, such rows of an earlier layer and a factor on the device: what is stored is
+// (1 - lambda) v + lambda v_first.  The table of cosines and sines may carry a common factor (the position
+// encoding's magnitude); the kernel's own sincosf path has none.
 #include "common.cuh"
 #include "api.h"
 
@@ -34,7 +39,9 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
                                           const int* __restrict__ block_table, int max_pages,
                                           AT* __restrict__ k_cache, AT* __restrict__ v_cache, int write_kv,
                                           const float2* __restrict__ cs_table, int vd, int hdp, int interleaved,
-                                          int n_gate, float* __restrict__ gate_out) {
+                                          int n_gate, float* __restrict__ gate_out, int post_norm,
+                                          const float* __restrict__ v_first, const float* __restrict__ v_lambda,
+                                          float* __restrict__ v_out) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -68,16 +75,16 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
     const IT* src = in + (size_t)t * row_stride + (kind == 2 ? (size_t)(nq + nkv) * hd + (size_t)head * vd : (size_t)h * hd);
     if (kind == 2) hd = vd;     // from here on: the width of this head in the row
 
-    AT* dst;
+    AT* dst = nullptr;
     if (kind == 0) {
         dst = q_out + (size_t)t * q_stride + (size_t)head * hdp;
     } else {
         const int page = block_table[(size_t)slot * max_pages + (pos / RB_PAGE)];
-        if (page < 0) return;  // no page: the host never schedules this; skip rather than fault
-        AT* base = (kind == 1 ? k_cache : v_cache);
-        dst = base + (((size_t)page * nkv + head) * RB_PAGE + (pos % RB_PAGE)) * hdp;
+        // no page: the host never schedules this; skip the cache rather than fault
+        if (page >= 0) dst = (kind == 1 ? k_cache : v_cache) + (((size_t)page * nkv + head) * RB_PAGE + (pos % RB_PAGE)) * hdp;
+        else if (kind == 1 || !v_out) return;
     }
-    for (int i = hd + lane; i < hdp; i += 32) dst[i] = from_f32<AT>(0.f);
+    if (dst) for (int i = hd + lane; i < hdp; i += 32) dst[i] = from_f32<AT>(0.f);
 
     float ss = 0.f;
     if (n_in > 1 && sizeof(IT) == 4 && (hd & 3) == 0 && (in_stride & 3) == 0 && (row_stride & 3) == 0 &&
@@ -113,13 +120,21 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
     }
     __syncwarp();
     if (kind == 2) {
-        for (int i = lane; i < hd; i += 32) dst[i] = from_f32<AT>(buf[i]);
+        const size_t vrow = ((size_t)t * nkv + head) * vd;
+        const float lam = v_first ? v_lambda[0] : 0.f;
+        for (int i = lane; i < hd; i += 32) {
+            float v = buf[i];
+            if (v_out) v_out[vrow + i] = v;
+            if (v_first) v = (1.f - lam) * v + lam * v_first[vrow + i];
+            if (dst) dst[i] = from_f32<AT>(v);
+        }
         return;
     }
     ss = warp_sum(ss);
     const WT* w = kind == 0 ? q_norm_w : k_norm_w;
     const float inv = w ? rsqrtf(ss / (float)hd + eps) : 1.f;
     const int half = inv_freq ? rot_dim / 2 : 0;
+    float ss2 = 0.f;         // the sum of squares after the rotation (a pair is one lane's: no lane reads another's)
     for (int i = lane; i < half; i += 32) {
         const int i0 = interleaved ? 2 * i : i, i1 = interleaved ? 2 * i + 1 : i + half;
         float x0 = buf[i0], x1 = buf[i1];
@@ -127,14 +142,19 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
         float sn, cs;
         if (cs_table) { const float2 c2 = cs_table[(size_t)t * half + i]; cs = c2.x; sn = c2.y; }
         else sincosf((float)pos * inv_freq[i], &sn, &cs);
-        dst[i0] = from_f32<AT>(x0 * cs - x1 * sn);
-        dst[i1] = from_f32<AT>(x0 * sn + x1 * cs);
+        const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
+        buf[i0] = y0; buf[i1] = y1;
+        ss2 += y0 * y0 + y1 * y1;
     }
     for (int i = 2 * half + lane; i < hd; i += 32) {
         float x = buf[i];
         if (w) x = x * inv * to_f32(w[i]);
-        dst[i] = from_f32<AT>(x);
+        buf[i] = x;
+        ss2 += x * x;
     }
+    __syncwarp();
+    const float inv2 = post_norm ? rsqrtf(warp_sum(ss2) / (float)hd + eps) : 1.f;
+    for (int i = lane; i < hd; i += 32) dst[i] = from_f32<AT>(buf[i] * inv2);
 }
 
 // The same for a head size of 128 with the whole head rotated, the common case: a lane holds 4
@@ -288,13 +308,14 @@ static int launch_qk(const void* in, int n_in, long long in_stride, int row_stri
                      int T, int nq, int nkv, int hd, const void* qw, const void* kw, float eps,
                      const float* inv_freq, int rot_dim, const int* positions, const int* slot_of_token,
                      const int* block_table, int max_pages, void* k_cache, void* v_cache, int write_kv,
-                     const float2* cs_table, int vd, int hdp, int interleaved, int n_gate, float* gate_out, cudaStream_t s) {
+                     const float2* cs_table, int vd, int hdp, int interleaved, int n_gate, float* gate_out, int post_norm,
+                     const float* v_first, const float* v_lambda, float* v_out, cudaStream_t s) {
     const int warps = 4;
     const long long items = (long long)T * (nq + (write_kv ? 2 * nkv : 0) + (n_gate > 0 ? 1 : 0));
     const long long blocks = (items + warps - 1) / warps;
     if (blocks > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
     const size_t esz = sizeof(IT);
-    if (hd == 128 && vd == 128 && hdp == 128 && n_gate == 0 && !(inv_freq && interleaved) &&
+    if (hd == 128 && vd == 128 && hdp == 128 && n_gate == 0 && !post_norm && !v_first && !v_out && !(inv_freq && interleaved) &&
         (!inv_freq || rot_dim == 128) && (((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)k_cache |
                                                         (uintptr_t)v_cache | (uintptr_t)qw | (uintptr_t)kw |
                                                         (uintptr_t)cs_table) & 15) == 0 &&
@@ -311,7 +332,8 @@ static int launch_qk(const void* in, int n_in, long long in_stride, int row_stri
     RB_LAUNCH((qk_norm_rope_cache_kernel<IT, AT, WT>), dim3((int)blocks), dim3(warps * 32), smem, s, (const IT*)in,
               n_in, (size_t)in_stride, row_stride, (AT*)q_out, q_stride, T, nq, nkv, hd, (const WT*)qw,
               (const WT*)kw, eps, inv_freq, rot_dim, positions, slot_of_token, block_table, max_pages,
-              (AT*)k_cache, (AT*)v_cache, write_kv, cs_table, vd, hdp, interleaved, n_gate, gate_out);
+              (AT*)k_cache, (AT*)v_cache, write_kv, cs_table, vd, hdp, interleaved, n_gate, gate_out, post_norm,
+              v_first, v_lambda, v_out);
     return RB_OK;
 }
 
@@ -321,18 +343,19 @@ extern "C" int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, lon
                                      const float* inv_freq, int rot_dim, const int* positions,
                                      const int* slot_of_token, const int* block_table, int max_pages,
                                      void* k_cache, void* v_cache, int write_kv, const void* cos_sin, int vd, int hdp,
-                                     int interleaved, int n_gate, float* gate_out, void* stream) {
+                                     int interleaved, int n_gate, float* gate_out, int post_norm, const float* v_first,
+                                     const float* v_lambda, float* v_out, void* stream) {
     if (T <= 0) return RB_OK;
     if (vd <= 0) vd = hd;
     if (hdp <= 0) hdp = hd > vd ? hd : vd;
     if (hd <= 0 || n_in < 1 || hdp < hd || hdp < vd || (inv_freq && (rot_dim <= 0 || rot_dim % 2 || rot_dim > hd)) ||
-        n_gate < 0 || (n_gate > 0 && !gate_out) || ((q_norm_w || k_norm_w) && vd != hd))
+        n_gate < 0 || (n_gate > 0 && !gate_out) || (v_first && !v_lambda) || ((v_first || v_out) && !write_kv))
         return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     typedef __nv_bfloat16 bf;
 #define RB_QK_ARGS in, n_in, in_stride, row_stride, q_out, q_stride, T, nq, nkv, hd, q_norm_w, k_norm_w, eps, \
                    inv_freq, rot_dim, positions, slot_of_token, block_table, max_pages, k_cache, v_cache, write_kv, \
-                   (const float2*)cos_sin, vd, hdp, interleaved, n_gate, gate_out, s
+                   (const float2*)cos_sin, vd, hdp, interleaved, n_gate, gate_out, post_norm, v_first, v_lambda, v_out, s
     if (in_dtype == RB_BF16 && act_dtype == RB_BF16 && w_dtype == RB_BF16) return launch_qk<bf, bf, bf>(RB_QK_ARGS);
     if (in_dtype == RB_BF16 && act_dtype == RB_BF16 && w_dtype == RB_F32) return launch_qk<bf, bf, float>(RB_QK_ARGS);
     if (in_dtype == RB_F32 && act_dtype == RB_BF16 && w_dtype == RB_BF16) return launch_qk<float, bf, bf>(RB_QK_ARGS);
@@ -343,10 +366,10 @@ extern "C" int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, lon
     return RB_ERR_BAD_DTYPE;
 }
 
-// cos and sin of pos * inv_freq[i] for every token of a step, [T][half] pairs (cos, sin): computed
-// once per step with full-precision sincosf and read by every layer's rotation.
+// cos and sin of pos * inv_freq[i] for every token of a step, [T][half] pairs (cos, sin), both times `mag`:
+// computed once per step with full-precision sincosf and read by every layer's rotation.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int T,
-                                  int half, float2* __restrict__ out) {
+                                  int half, float mag, float2* __restrict__ out) {
     pdl_trigger();
     pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -354,14 +377,15 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     const int t = idx / half, i = idx - t * half;
     float sn, cs;
     sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
-    out[idx] = make_float2(cs, sn);
+    out[idx] = make_float2(cs * mag, sn * mag);
 }
 
-extern "C" int rb_rope_table(const int* positions, const float* inv_freq, int T, int half, void* out, void* stream) {
+extern "C" int rb_rope_table(const int* positions, const float* inv_freq, int T, int half, float mag, void* out,
+                             void* stream) {
     if (T <= 0 || half <= 0) return RB_OK;
     const long long n = (long long)T * half;
     if (n > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((rope_table_kernel), dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, positions,
-              inv_freq, T, half, (float2*)out);
+              inv_freq, T, half, mag, (float2*)out);
     return RB_OK;
 }

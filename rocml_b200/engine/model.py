@@ -39,6 +39,8 @@ class Model:
                                        mixer_spec.position)
             self.blocks.append(build_block_with(layer, spec.hidden, env, mixer_spec))
         self.final_norm = build_norm(spec.final_norm, spec.hidden, env)
+        # a norm of the embedding output: what enters the first layer, and the stream itself, is the normalised row
+        self.embedding_norm = build_norm(spec.embedding_norm, spec.hidden, env) if spec.embedding_norm is not None else None
         self.head = Linear([spec.head_name[: -len(".weight")]], [spec.vocab], spec.hidden, False, env)
         self.embed: Optional[torch.Tensor] = None
         self.status: Optional[torch.Tensor] = None
@@ -63,13 +65,15 @@ class Model:
     # the stem, or nothing (``ModelSpec.weight_suffix``).  ``declare`` speaks the files' names, ``load``
     # takes them and hands the parts theirs.
     def _file_name(self, name: str) -> str:
-        suffix = self.spec.weight_suffix
-        if suffix != ".weight" and name.endswith(".weight"):
-            return name[: -len(".weight")] + suffix
+        for ours, theirs in ((".weight", self.spec.weight_suffix), (".bias", self.spec.bias_suffix)):
+            if theirs != ours and name.endswith(ours):
+                return name[: -len(ours)] + theirs
         return name
 
     def _declare_parts(self) -> List[TensorDecl]:
         out = [TensorDecl(self.spec.embedding_name, (self.vocab, self.hidden), "matrix")]
+        if self.embedding_norm is not None:
+            out += self.embedding_norm.declare(self.spec.embedding_norm_name[: -len(".weight")])
         for name, rows in self.added_rows.items():
             out.append(TensorDecl(name, (rows, self.hidden), "matrix"))
         for b in self.blocks:
@@ -85,12 +89,17 @@ class Model:
     def ignorable(self) -> List[str]:
         """Tensors a folder may hold that the model does not read: a stored head when the
         head is tied to the embedding."""
-        return [self._file_name(self.spec.head_name)] if self.spec.tie_embeddings else []
+        out = [self.spec.head_name] if self.spec.tie_embeddings else []
+        for b in self.blocks:
+            out += getattr(b, "ignorable", lambda: [])()
+        return [self._file_name(n) for n in out]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        if self.spec.weight_suffix != ".weight":
+        if self.spec.weight_suffix != ".weight" or self.spec.bias_suffix != ".bias":
             tensors = {d.name: tensors[self._file_name(d.name)] for d in self._declare_parts()}
         self.embed = tensors[self.spec.embedding_name]
+        if self.embedding_norm is not None:
+            self.embedding_norm.load(tensors, self.spec.embedding_norm_name[: -len(".weight")])
         self.added = {name: tensors[name] for name in self.added_rows}
         for b in self.blocks:
             b.load(tensors)
@@ -118,7 +127,8 @@ class Model:
     # ---- facts ----------------------------------------------------------------------------------
     @property
     def graph_safe(self) -> bool:
-        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe and \
+            (self.embedding_norm is None or self.embedding_norm.graph_safe)
 
     def cache_requirements(self):
         return [self.blocks[e.layer].mixer.cache_requirement() for e in self.spec.schedule]
@@ -153,20 +163,29 @@ class Model:
                 b, f = block.weight_bytes(), 0
             nbytes, flops = nbytes + b, flops + f
         hb, hf = self.head.cost(n_want)
-        return nbytes + self.final_norm.weight_bytes() + hb, flops + hf
+        nb = self.embedding_norm.weight_bytes() if self.embedding_norm is not None else 0
+        return nbytes + self.final_norm.weight_bytes() + nb + hb, flops + hf
 
     # ---- the pass ---------------------------------------------------------------------------------
     def forward(self, batch, cache) -> Optional[torch.Tensor]:
         T = batch.n_tokens
         resid = torch.empty((T, self.hidden), dtype=torch.float32, device=self.env.device)
         x0 = torch.empty_like(resid) if self.keeps_input else None
+        # with a norm of the embedding output the gathered rows land beside the stream, and the norm writes the stream
+        rows = torch.empty_like(resid) if self.embedding_norm is not None else resid
         with scope(op="embedding"):
-            if self.input_position is None and self.spec.embedding_scale == 1.0 and x0 is None:
-                kernels.embedding(batch.token_ids, self.embed, resid, self.status)
+            if self.input_position is None and self.spec.embedding_scale == 1.0 and (x0 is None or rows is not resid):
+                kernels.embedding(batch.token_ids, self.embed, rows, self.status)
             else:
-                kernels.embedding_pos(batch.token_ids, self.embed, resid, self.spec.embedding_scale, batch.positions,
+                kernels.embedding_pos(batch.token_ids, self.embed, rows, self.spec.embedding_scale, batch.positions,
                                       self.input_position.inv_freq if self.input_position is not None else None,
-                                      copy=x0, status=self.status)
+                                      copy=x0 if rows is resid else None, status=self.status)
+        if self.embedding_norm is not None:
+            with scope(op="embedding_norm"):
+                kernels.add_rmsnorm(rows, None, self.embedding_norm.weight, self.embedding_norm.eps, resid, n_rows=T,
+                                    write_back=False)
+                if x0 is not None:
+                    x0.copy_(resid)
         pending = None
         sched = self.spec.schedule
         for i, e in enumerate(sched):

@@ -126,16 +126,17 @@ def _lib():
     lib = library()
     if not _sigs_done:
         lib.rb_embedding.argtypes = [_vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp]
-        lib.rb_add_rmsnorm.argtypes = [_vp, _vp, _i, _ll, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _vp]
+        lib.rb_add_rmsnorm.argtypes = [_vp, _vp, _i, _ll, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _vp, _vp, _vp]
         lib.rb_silu_mul.argtypes = [_vp, _i, _i, _ll, _vp, _i, _i, _i, _i, _vp]
         lib.rb_cast.argtypes = [_vp, _i, _vp, _i, _ll, _vp]
         lib.rb_qk_norm_rope_cache.argtypes = [_vp, _i, _i, _ll, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f,
-                                              _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp]
-        lib.rb_rope_table.argtypes = [_vp, _vp, _i, _i, _vp, _vp]
+                                              _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _vp,
+                                              _vp, _vp, _vp]
+        lib.rb_rope_table.argtypes = [_vp, _vp, _i, _i, _f, _vp, _vp]
         lib.rb_gemm_generic.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _vp]
         lib.rb_attention_generic.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i,
-                                             _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp]
-        lib.rb_attention_merge.argtypes = [_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
+                                             _i, _i, _i, _f, _i, _i, _f, _i, _i, _vp, _vp, _vp]
+        lib.rb_attention_merge.argtypes = [_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp]
         lib.rb_argmax.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _i, _vp]
         lib.rb_attention_prefill.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                              _f, _i, _vp]
@@ -170,7 +171,7 @@ def _lib():
         lib.rb_moe_combine.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _ll, _vp, _i, _vp]
         lib.rb_grouped_matmul.argtypes = [_vp, _i, _ll, _i, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _vp, _i,
                                           _vp, _i, _i, _f, _f, _vp]
-        lib.rb_head_gate.argtypes = [_vp, _ll, _i, _vp, _ll, _i, _vp, _i, _i, _i, _vp]
+        lib.rb_head_gate.argtypes = [_vp, _ll, _i, _vp, _ll, _i, _vp, _i, _vp, _i, _i, _ll, _ll, _i, _i, _i, _vp]
         lib.rb_decay_scan.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _i,
                                       _vp, _i, _vp]
         lib.rb_decay_step.argtypes = lib.rb_decay_scan.argtypes
@@ -207,10 +208,12 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status:
     bool(a["write_back"]) and a["delta"] is not None, _esz(a["weight"])))
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
-                write_back: bool = True):
+                write_back: bool = True, weight2: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None):
     """resid [T, H] float32 (+= sum of delta [S, T, H] float32); out[i] = rmsnorm(row) * weight.
 
-    With ``rows`` (int32 indices, -1 = skip) output row i comes from source row rows[i]."""
+    With ``rows`` (int32 indices, -1 = skip) output row i comes from source row rows[i].  ``weight2`` and
+    ``out2`` (like ``weight`` and ``out``): a second norm of the same rows with the same eps, whose output differs
+    by its weight only."""
     T, H = resid.shape
     if resid.dtype != torch.float32 or not resid.is_contiguous() or not out.is_contiguous():
         raise KernelError("add_rmsnorm: resid must be contiguous float32, out contiguous")
@@ -223,9 +226,14 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     n = (rows.numel() if rows is not None else T) if n_rows is None else n_rows
     if out.shape[-1] != H or out.numel() < n * H or weight.numel() != H:
         raise KernelError("add_rmsnorm: shapes do not fit")
+    if (weight2 is None) != (out2 is None):
+        raise KernelError("add_rmsnorm: a second weight comes with a second output")
+    if weight2 is not None and (weight2.dtype != weight.dtype or weight2.numel() != H or out2.dtype != out.dtype or
+                                not out2.is_contiguous() or out2.shape != out.shape):
+        raise KernelError("add_rmsnorm: the second weight and output must look like the first")
     rc = _lib().rb_add_rmsnorm(_ptr(resid), _ptr(delta), n_delta, stride, _ptr(weight), dtype_code(weight.dtype),
                                _ptr(out), dtype_code(out.dtype), None if rows is None else _i32(rows, "rows"),
-                               n, H, float(eps), 1 if write_back else 0, _stream())
+                               n, H, float(eps), 1 if write_back else 0, _ptr(weight2), _ptr(out2), _stream())
     _check(rc, "add_rmsnorm")
 
 
@@ -270,21 +278,26 @@ def qk_norm_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, n_tokens: int, n
                        k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], write_kv: bool = True,
                        cos_sin: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
                        padded_head_dim: Optional[int] = None, interleaved: bool = False,
-                       gates: Optional[torch.Tensor] = None):
+                       gates: Optional[torch.Tensor] = None, post_norm: bool = False,
+                       v_first: Optional[torch.Tensor] = None, v_lambda: Optional[torch.Tensor] = None,
+                       v_out: Optional[torch.Tensor] = None):
     """``cos_sin`` (from rope_table, float32 [T, rot_dim / 2, 2]) replaces the kernel's own sincosf.
     proj [T, nq*hd (+ nkv*hd + nkv*vd) (+ gates)] (or [S, T, ...] partial sums): q normalised and rotated into
     q_out (rows of nq*hdp, any row stride; it may be ``proj`` itself when nothing is padded); k (normalised,
     rotated) and v written to their pages.  ``v_head_dim`` (vd): the value heads' width when it is not hd;
     ``padded_head_dim`` (hdp): the width of every head in q_out and in the cache (zeros beyond a head's own);
     ``interleaved``: rotation pairs are neighbours (2i, 2i + 1) instead of (i, i + rot_dim / 2); ``gates``
-    (float32 [T, n]): the sigmoid of the row's last n columns."""
+    (float32 [T, n]): the sigmoid of the row's last n columns.  ``post_norm``: q and k are divided by their root
+    mean square over the head (eps inside the root, no weight) after the rotation.  ``v_out`` (float32 [T, nkv * vd])
+    receives the value heads as projected; ``v_first`` (such rows of an earlier layer) and ``v_lambda`` (float32,
+    one number on the device): the cache receives (1 - lambda) v + lambda v_first."""
     vd = hd if v_head_dim is None else int(v_head_dim)
     hdp = max(hd, vd) if padded_head_dim is None else int(padded_head_dim)
     n_gate = 0 if gates is None else gates.shape[-1]
     width = nq * hd + (nkv * (hd + vd) if write_kv else 0)
     n_in, in_stride, row_stride = _partials(proj, "qk_norm_rope_cache")
-    if proj.shape[-1] < width + n_gate or (n_gate == 0 and hdp == hd and proj.shape[-1] != width):
-        raise KernelError(f"qk_norm_rope_cache: projections must be {width + n_gate} wide")
+    if proj.shape[-1] < width + n_gate:
+        raise KernelError(f"qk_norm_rope_cache: projections must be at least {width + n_gate} wide")
     if gates is not None and (gates.dtype != torch.float32 or not gates.is_contiguous() or gates.shape[0] < n_tokens):
         raise KernelError("qk_norm_rope_cache: gates must be contiguous float32 [T, n]")
     if q_out.stride(-1) != 1 or q_out.shape[-1] < nq * hdp:
@@ -304,22 +317,30 @@ def qk_norm_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, n_tokens: int, n
         if k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype or not k_cache.is_contiguous() or \
                 tuple(k_cache.shape[1:]) != (nkv, PAGE, hdp):
             raise KernelError("qk_norm_rope_cache: cache must be [pages, nkv, 64, hdp] of the activations' type")
+    for name, t in (("v_first", v_first), ("v_out", v_out)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.shape[0] < n_tokens or
+                              t.shape[-1] != nkv * vd or not write_kv):
+            raise KernelError(f"qk_norm_rope_cache: {name} must be contiguous float32 [T, nkv * vd] of a layer that writes its cache")
+    if (v_first is None) != (v_lambda is None) or (v_lambda is not None and (v_lambda.dtype != torch.float32 or v_lambda.numel() != 1)):
+        raise KernelError("qk_norm_rope_cache: v_first comes with v_lambda, one float32 number")
     max_pages = block_table.shape[1] if block_table is not None else 0
     rc = _lib().rb_qk_norm_rope_cache(
         _ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, _ptr(q_out), dtype_code(q_out.dtype),
         q_out.stride(-2), n_tokens, nq, nkv, hd, _ptr(q_norm_w), _ptr(k_norm_w), wd, float(eps), _ptr(inv_freq),
         rot_dim, _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"),
         None if block_table is None else _i32(block_table, "block_table"), max_pages, _ptr(k_cache), _ptr(v_cache),
-        1 if write_kv else 0, _ptr(cos_sin), vd, hdp, 1 if interleaved else 0, n_gate, _ptr(gates), _stream())
+        1 if write_kv else 0, _ptr(cos_sin), vd, hdp, 1 if interleaved else 0, n_gate, _ptr(gates),
+        1 if post_norm else 0, _ptr(v_first), _ptr(v_lambda), _ptr(v_out), _stream())
     _check(rc, "qk_norm_rope_cache")
 
 
 @_profiled(lambda a, facts: _cost.rope_table(a["n_tokens"], a["inv_freq"].numel()))
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, n_tokens: int) -> torch.Tensor:
-    """float32 [T, half, 2]: (cos, sin) of positions[t] * inv_freq[i], full-precision sincosf."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, n_tokens: int, magnitude: float = 1.0) -> torch.Tensor:
+    """float32 [T, half, 2]: (cos, sin) of positions[t] * inv_freq[i], full-precision sincosf, both times ``magnitude``."""
     half = inv_freq.numel()
     out = torch.empty((n_tokens, half, 2), dtype=torch.float32, device=inv_freq.device)
-    _check(_lib().rb_rope_table(_i32(positions, "positions"), _ptr(inv_freq), n_tokens, half, _ptr(out), _stream()),
+    _check(_lib().rb_rope_table(_i32(positions, "positions"), _ptr(inv_freq), n_tokens, half, float(magnitude), _ptr(out),
+                                _stream()),
            "rope_table")
     return out
 
@@ -361,8 +382,10 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                       n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
                       chunk: int = 0, n_chunks: int = 1, part_acc: Optional[torch.Tensor] = None,
-                      part_ml: Optional[torch.Tensor] = None):
-    """q rows [T, >= nq*hd] (row stride free) -> out rows [T, >= nq*hd]; keys and values from the pages."""
+                      part_ml: Optional[torch.Tensor] = None, keep: int = 0, sink: Optional[float] = None):
+    """q rows [T, >= nq*hd] (row stride free) -> out rows [T, >= nq*hd]; keys and values from the pages.
+    ``keep``: the keys at positions below it stay visible beside the window; ``sink``: a score that adds
+    exp(sink) to every row's denominator and brings no value (None: no such term)."""
     if q.stride(-1) != 1 or out.stride(-1) != 1 or q.dtype != out.dtype or k_cache.dtype != q.dtype:
         raise KernelError("attention_generic: strides or types do not fit")
     if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
@@ -370,9 +393,16 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     rc = _lib().rb_attention_generic(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), dtype_code(q.dtype), _ptr(k_cache), _ptr(v_cache),
         _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"),
-        _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window), int(chunk),
-        int(n_chunks), _ptr(part_acc), _ptr(part_ml), _stream())
+        _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window), int(keep), _sink(sink),
+        int(chunk), int(n_chunks), _ptr(part_acc), _ptr(part_ml), _stream())
     _check(rc, "attention_generic")
+
+
+NO_SINK = -3.0e38     # RB_NO_SINK of csrc/common.cuh
+
+
+def _sink(sink: Optional[float]) -> float:
+    return NO_SINK if sink is None else float(sink)
 
 
 PREFILL_L2_BYTES = 96 << 20     # keys and values that stay in the 126 MB L2 cache beside everything else
@@ -574,10 +604,10 @@ def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch
 @_profiled(lambda a, facts: (a["part_acc"].numel() * 4 + a["part_ml"].numel() * 4 + a["n_tokens"] * a["nq"] * a["hd"] * _esz(a["out"]), 0))
 def attention_merge(part_acc: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
                     slot_of_token: torch.Tensor, n_tokens: int, nq: int, hd: int, chunk: int, n_chunks: int,
-                    window: int = 0):
+                    window: int = 0, keep: int = 0, sink: Optional[float] = None):
     rc = _lib().rb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), out.stride(0), dtype_code(out.dtype),
                                    _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"), n_tokens,
-                                   nq, hd, chunk, n_chunks, int(window), _stream())
+                                   nq, hd, chunk, n_chunks, int(window), int(keep), _sink(sink), _stream())
     _check(rc, "attention_merge")
 
 
@@ -1181,16 +1211,26 @@ def group_norm_gate(o: torch.Tensor, proj: torch.Tensor, g_off: int, weight: Opt
 
 
 @_profiled(lambda a, facts: (a["n_tokens"] * a["heads"] * (a["in_w"] + a["out_w"]) * _esz(a["x"]), a["n_tokens"] * a["heads"] * a["out_w"]))
-def head_gate(x: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], heads: int, in_w: int, out_w: int, n_tokens: int):
-    """out[t, h, :out_w] = x[t, h, :out_w] * gate[t, h]: an attention result's heads (``in_w`` wide, of which
-    ``out_w`` are values and the rest padding) times a float32 gate a head (None: 1)."""
+def head_gate(x: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], heads: int, in_w: int, out_w: int, n_tokens: int,
+              raw: Optional[torch.Tensor] = None, per_value: bool = False):
+    """out[t, h, :out_w] = x[t, h, :out_w] * gate: an attention result's heads (``in_w`` wide, of which ``out_w`` are
+    values and the rest padding) times a gate formed in 32-bit.  ``gate``: float32 [T, heads] (one a head) or, with
+    ``per_value``, [T, heads * out_w] (one a value).  ``raw`` instead: such columns of the projection rows ([T, n] or
+    [S, T, n] partial sums, any row stride), of which the kernel takes the sigmoid.  Neither: the heads are only narrowed."""
     if x.dtype != out.dtype or x.stride(-1) != 1 or out.stride(-1) != 1 or x.shape[-1] < heads * in_w or \
             out.shape[-1] < heads * out_w:
         raise KernelError("head_gate: shapes or types do not fit")
-    if gate is not None and (gate.dtype != torch.float32 or not gate.is_contiguous() or gate.shape[-1] != heads):
-        raise KernelError("head_gate: gate must be contiguous float32 [T, heads]")
-    _check(_lib().rb_head_gate(_ptr(x), x.stride(0), in_w, _ptr(out), out.stride(0), out_w, _ptr(gate), heads, n_tokens,
-                               dtype_code(x.dtype), _stream()), "head_gate")
+    gate_w = out_w if per_value else 1
+    if gate is not None and (gate.dtype != torch.float32 or not gate.is_contiguous() or gate.shape[-1] != heads * gate_w):
+        raise KernelError("head_gate: gate must be contiguous float32 [T, heads] or [T, heads * out_w]")
+    n_in, in_stride, row_stride = 1, 0, 0
+    if raw is not None:
+        if gate is not None or raw.stride(-1) != 1 or raw.shape[-1] != heads * gate_w:
+            raise KernelError("head_gate: raw gate columns must be [.., T, heads (* out_w)] with unit stride, and no finished gate beside them")
+        n_in, in_stride, row_stride = (raw.shape[0], raw.stride(0), raw.stride(1)) if raw.dim() == 3 else (1, 0, raw.stride(0))
+    _check(_lib().rb_head_gate(_ptr(x), x.stride(0), in_w, _ptr(out), out.stride(0), out_w, _ptr(gate), gate_w, _ptr(raw),
+                               dtype_code(raw.dtype) if raw is not None else F32, n_in, in_stride, row_stride, heads,
+                               n_tokens, dtype_code(x.dtype), _stream()), "head_gate")
 
 
 # ---- many small products in one launch ----------------------------------------------------------------------------

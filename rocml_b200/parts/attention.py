@@ -10,7 +10,12 @@ Sizes and constants (heads, groups, head size, biases, q/k norm and its eps, win
 are parameters; a layer that reads another layer's cache projects only q.  Further parameters:
 value heads of another size than the key heads (``v_head_dim``), a mask by blocks of positions
 instead of a window (``chunk``), a sigmoid gate per head on the attention's result, read from the
-layer's input (``gated``), and, through the position encoding, rotation by neighbouring pairs.
+layer's input (``gated``; "per_value": a gate for every value of every head), and, through the
+position encoding, rotation by neighbouring pairs.  Beside a window, the first ``keep_first`` positions
+may stay visible to every later query; the softmax's denominator may have one more term exp(``sink``)
+that brings no value; queries and keys may be divided by their root mean square after the position
+encoding (``qk_unit_norm``); biases may be given for some of the projections only; and the values that
+a layer caches may be blended with those of an earlier layer of the same step (``value_mix``).
 Heads of unequal or odd sizes are written into the cache padded with zeros to one width that the
 attention kernels take: zeros in queries and keys change no score, zeros in values give zeros
 that are dropped before the output projection.
@@ -40,7 +45,9 @@ PROMPT_FUSED_MIN_TOKENS = 4096
 # Tensor-name stems by role, unless the spec's ``names`` says otherwise (the defaults are those of
 # Hugging Face's Qwen3 checkpoints: rocml/src/weights/layer.rs:47-58 lists the same tensors under GGUF names).
 TENSOR_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm",
-                "gate": "gate_proj"}
+                "gate": "gate_proj", "value_mix": "value_mix"}
+
+VALUE_MIX_SOURCE = "attention.value_mix_source"    # where a step keeps the source layer's values (StepBatch.scratch)
 
 DECODE_CHUNK = 64   # keys per split of decode attention (one page); fixed, so a row's sums never depend on the batch
 
@@ -60,14 +67,24 @@ class Attention(Mixer):
             raise ConfigError(f"{self.nq} query heads cannot be grouped over {self.nkv} key/value heads")
         self.vd = int(p.get("v_head_dim") or self.hd)
         self.gated = bool(p.get("gated", False))
+        self.gate_per_value = p.get("gated") == "per_value"
         self.hdp = -(-max(self.hd, self.vd) // 16) * 16         # the width of every head in the cache
         if min(self.hd, self.vd) <= 0 or self.hdp > 512:
             raise ConfigError(f"head sizes {self.hd} (keys) and {self.vd} (values) are not supported: 1 to 512")
-        self.bias = bool(p.get("bias", False))
+        bias = p.get("bias", False)
+        self.bias = bool(bias)
         self.qk_norm = bool(p.get("qk_norm", False))
         self.qk_norm_eps = float(p.get("qk_norm_eps", 1e-6))
+        self.qk_unit_norm = bool(p.get("qk_unit_norm", False))
         self.window = p.get("window")
         self.chunk = p.get("chunk")
+        self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
+        self.sink = None if p.get("sink") is None else float(p["sink"])
+        self.value_mix = p.get("value_mix")
+        if self.value_mix not in (None, "source", "mix"):
+            raise ConfigError(f"attention: value_mix is 'source' or 'mix', found {self.value_mix!r}")
+        if self.keep_first < 0:
+            raise ConfigError("attention: keep_first counts positions and cannot be negative")
         if self.window and self.chunk:
             raise ConfigError("attention: a layer has a window or blocks of positions, not both")
         if (self.window is not None and int(self.window) < 1) or (self.chunk is not None and int(self.chunk) < 1):
@@ -77,29 +94,36 @@ class Attention(Mixer):
         self.position = build_position(spec.position, self.hd, env)
         # the plain layout: equal head sizes that the kernels take as they are, rotate-half pairs, no gate
         self.plain = self.vd == self.hd == self.hdp and not self.gated and \
-            not (self.position.inv_freq is not None and getattr(self.position, "interleaved", False))
+            not (self.position.inv_freq is not None and getattr(self.position, "interleaved", False)) and \
+            not (self.keep_first or self.sink is not None or self.qk_unit_norm or self.value_mix)
         if not self.plain and self.shares_cache:
             raise ConfigError("attention: a layer that reads another layer's cache must have the plain layout")
-        if self.qk_norm and self.vd != self.hd:
-            raise ConfigError("attention: q/k norms with value heads of another size are not built")
         qd, kvd = self.nq * self.hd, self.nkv * self.hd
         try:
             self.names = n = tensor_names(p, TENSOR_NAMES)
         except ValueError as e:
             raise ConfigError(f"attention: {e}") from None
+        if not isinstance(bias, bool):          # the roles that have a bias, by name
+            unknown = sorted(set(bias) - {"q", "k", "v", "o", "gate"})
+            if unknown:
+                raise ConfigError(f"attention: biases for unknown projections {unknown}")
+            in_bias, o_bias = [n[r] for r in bias if r != "o"], "o" in bias
+        else:
+            in_bias, o_bias = bias, bias
         if self.shares_cache:
-            self.qkv = Linear([n["q"]], [qd], hidden, self.bias, env)
+            self.qkv = Linear([n["q"]], [qd], hidden, in_bias, env)
         else:
             stems, outs = [n["q"], n["k"], n["v"]], [qd, kvd, self.nkv * self.vd]
             if self.gated:
-                stems, outs = stems + [n["gate"]], outs + [self.nq]
-            self.qkv = Linear(stems, outs, hidden, self.bias, env)
-        self.o = Linear([n["o"]], [hidden], self.nq * self.vd, self.bias, env)
+                stems, outs = stems + [n["gate"]], outs + [self.nq * self.vd if self.gate_per_value else self.nq]
+            self.qkv = Linear(stems, outs, hidden, in_bias, env)
+        self.o = Linear([n["o"]], [hidden], self.nq * self.vd, o_bias, env)
         self.q_norm_w: Optional[torch.Tensor] = None
         self.k_norm_w: Optional[torch.Tensor] = None
+        self.v_lambda: Optional[torch.Tensor] = None     # float32 [1] on the device: the share of the source layer's values
 
     def cache_requirement(self):
-        return KVRequirement(self.nkv, self.hdp, self.window, chunk=self.chunk)
+        return KVRequirement(self.nkv, self.hdp, self.window, chunk=self.chunk, keep_first=self.keep_first)
 
     def _span(self) -> int:
         """The mask as the kernels take it: 0 every earlier key, n the last n keys, -n blocks of n positions."""
@@ -113,7 +137,13 @@ class Attention(Mixer):
             out.append(TensorDecl(f"{prefix}{self.names['q_norm']}.weight", (self.hd,), "norm"))
             if not self.shares_cache:
                 out.append(TensorDecl(f"{prefix}{self.names['k_norm']}.weight", (self.hd,), "norm"))
+        if self.value_mix == "mix":
+            out.append(TensorDecl(f"{prefix}{self.names['value_mix']}.weight", (), "fraction"))
         return out
+
+    def ignorable(self, prefix: str) -> List[str]:
+        """A layer that does not blend its values may still carry the blend's number in the files."""
+        return [] if self.value_mix == "mix" else [f"{prefix}{self.names['value_mix']}.weight"]
 
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
         self.qkv.load(tensors, prefix)
@@ -125,6 +155,8 @@ class Attention(Mixer):
             self.k_norm_w = self.q_norm_w if self.shares_cache else tensors[f"{prefix}{self.names['k_norm']}.weight"]
             if self.k_norm_w.dtype != self.q_norm_w.dtype:
                 self.q_norm_w, self.k_norm_w = self.q_norm_w.float(), self.k_norm_w.float()
+        if self.value_mix == "mix":
+            self.v_lambda = tensors[f"{prefix}{self.names['value_mix']}.weight"].float().reshape(1).contiguous()
 
     def weight_bytes(self) -> int:
         return self.qkv.weight_bytes() + self.o.weight_bytes()
@@ -204,20 +236,35 @@ class Attention(Mixer):
             xn = xn.materialize()
         proj = self.qkv.forward_auto(xn, T)
         q = torch.empty((T, self.nq * self.hdp), dtype=act, device=dev)
-        gates = torch.empty((T, self.nq), dtype=torch.float32, device=dev) if self.gated else None
+        gates = torch.empty((T, self.nq), dtype=torch.float32, device=dev) if self.gated and not self.gate_per_value else None
+        # values blended across layers: the source layer leaves its own for the step's later layers
+        v_out = v_first = None
+        if self.value_mix == "source":
+            v_out = batch.scratch[VALUE_MIX_SOURCE] = torch.empty((T, self.nkv * self.vd), dtype=torch.float32, device=dev)
+        elif self.value_mix == "mix":
+            v_first = batch.scratch.get(VALUE_MIX_SOURCE)
+            if v_first is None or v_first.shape != (T, self.nkv * self.vd):
+                raise ConfigError("attention: a layer blends its values with a source layer's, which must run before it "
+                                  "in the same step with the same key/value heads and value size")
         with scope(op="rotate_cache"):
             kernels.qk_norm_rope_cache(
                 proj, q, T, self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
                 self.position.inv_freq, self.position.rot_dim, batch.positions, batch.slot_of_token,
                 view.block_table, view.k, view.v, write_kv=writes, cos_sin=self.position.cos_sin(batch),
                 v_head_dim=self.vd, padded_head_dim=self.hdp, interleaved=getattr(self.position, "interleaved", False),
-                gates=gates)
+                gates=gates, post_norm=self.qk_unit_norm, v_first=v_first, v_lambda=self.v_lambda if v_first is not None else None,
+                v_out=v_out)
         attn = torch.empty((T, self.nq * self.hdp), dtype=act, device=dev)
-        paged_attention(q, attn, batch, view.k, view.v, view.block_table, self.nq, self.nkv, self.hdp, self.scale, window)
+        paged_attention(q, attn, batch, view.k, view.v, view.block_table, self.nq, self.nkv, self.hdp, self.scale, window,
+                        keep=self.keep_first, sink=self.sink)
         if self.gated or self.hdp != self.vd:
             narrow = torch.empty((T, self.nq * self.vd), dtype=act, device=dev)
+            raw = None
+            if self.gate_per_value:          # the gate's columns of the projection rows, as they are: the kernel takes the sigmoid
+                off = self.nq * self.hd + self.nkv * (self.hd + self.vd)
+                raw = proj[..., off:off + self.nq * self.vd]
             with scope(op="head_gate"):
-                kernels.head_gate(attn, narrow, gates, self.nq, self.hdp, self.vd, T)
+                kernels.head_gate(attn, narrow, gates, self.nq, self.hdp, self.vd, T, raw=raw, per_value=self.gate_per_value)
             attn = narrow
         if sink is not None:
             deferred = self.o.forward_residual(attn, T, sink)
@@ -280,11 +327,13 @@ class Attention(Mixer):
         paged_attention(q, out, batch, view.k, view.v, view.block_table, self.nq, self.nkv, self.hd, self.scale, window)
 
 
-def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window):
+def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window, keep=0, sink=None):
     """Softmax attention of the step's queries (rows of nq heads of ``hd``) over paged keys and values
-    [pages, nkv, 64, hd], causal, inside ``window`` when it is not 0.  One token per sequence:
+    [pages, nkv, 64, hd], causal, inside ``window`` when it is not 0 (and the first ``keep`` positions beside it);
+    ``sink``: a score whose exponential joins every row's denominator.  One token per sequence:
     keys split in fixed chunks, partial results merged; otherwise whole rows.  Any mixer whose cache is
     such pages calls this (keys and values may be the same tensor)."""
+    special = bool(keep) or sink is not None      # what only the plain kernel takes so far
     if batch.is_decode:
         chunk = DECODE_CHUNK
         T = batch.n_tokens
@@ -296,27 +345,27 @@ def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, s
             parts = max(n_pages, n_blocks)
             acc = torch.empty((T, nq, parts, hd), dtype=torch.float32, device=q.device)
             ml = torch.empty((T, nq, parts, 2), dtype=torch.float32, device=q.device)
-        fast = kernels.attention_decode(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
-                                        batch.kv_len, batch.n_seqs, nq, nkv, hd, scale,
-                                        window, n_blocks, acc, ml, ppb)
+        fast = not special and kernels.attention_decode(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
+                                                        batch.kv_len, batch.n_seqs, nq, nkv, hd, scale,
+                                                        window, n_blocks, acc, ml, ppb)
         n_chunks = n_pages
         if fast:
             return
         if n_chunks > 1:
             kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                                       batch.kv_len, batch.n_seqs, 1, nq, nkv, hd, scale,
-                                      window, chunk, n_chunks, acc, ml)
+                                      window, chunk, n_chunks, acc, ml, keep=keep, sink=sink)
             kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, nq, hd,
-                                    chunk, n_chunks, window)
+                                    chunk, n_chunks, window, keep=keep, sink=sink)
             return
-    if kernels.attention_prefill_tc5(q, batch.n_tokens, out, k_cache, v_cache, block_table, batch.seq_slot,
+    if not special and kernels.attention_prefill_tc5(q, batch.n_tokens, out, k_cache, v_cache, block_table, batch.seq_slot,
                                      batch.cu_q, batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv,
                                      hd, scale, window, max_kv_len=batch.max_kv_len):
         return
-    if kernels.attention_prefill(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
-                                 batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
-                                 scale, window):
+    if not special and kernels.attention_prefill(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
+                                                 batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
+                                                 scale, window):
         return
     kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                               batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
-                              scale, window)
+                              scale, window, keep=keep, sink=sink)

@@ -111,6 +111,10 @@ class Part:
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
         pass
 
+    def ignorable(self, prefix: str) -> List[str]:
+        """Tensors a folder may hold under this part's prefix that the part does not read."""
+        return []
+
     def weight_bytes(self) -> int:
         """Bytes of weights one forward pass reads (for the roofline)."""
         return 0

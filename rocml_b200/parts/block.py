@@ -247,6 +247,9 @@ class ParallelBlock:
     def declare(self) -> List[TensorDecl]:
         return [d for part, name in self._parts() for d in part.declare(name)]
 
+    def ignorable(self) -> List[str]:
+        return [n for part, name in self._parts() for n in getattr(part, "ignorable", lambda prefix: [])(name)]
+
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         for part, name in self._parts():
             part.load(tensors, name)
@@ -267,14 +270,21 @@ class ParallelBlock:
         parts = [part.cost(q_lens, kv_lens) for part, _ in self._parts()]
         return sum(p[0] for p in parts), sum(p[1] for p in parts)
 
-    def forward(self, resid, pending, batch, view):
-        from .. import kernels
-        T = batch.n_tokens
-        adds = not batch.is_decode and T > ADD_INTO_MIN_TOKENS and _defer_enabled()
+    def _normed(self, resid, pending, T):
+        """(the mixer's input, the feed-forward's input): here the same rows."""
         with scope(op="mixer_norm"):
             xn = self.norm.forward(resid, pending, T)        # adds what the layer before left, then normalises
         if isinstance(xn, DeferredNorm):
             xn = xn.materialize()
+        return xn, xn
+
+    def forward(self, resid, pending, batch, view):
+        from .. import kernels
+        T = batch.n_tokens
+        adds = not batch.is_decode and T > ADD_INTO_MIN_TOKENS and _defer_enabled()
+        xn, xf = self._normed(resid, pending, T)
+        # Both sublayers read the stream as it was before either: with the offer to add into the stream inside
+        # their last product, the feed-forward's input is formed before the mixer adds.
         if adds and getattr(self.mixer, "can_add_into", False):
             delta = self.mixer.forward(xn, batch, view, add_into=resid)
         else:
@@ -285,5 +295,37 @@ class ParallelBlock:
             with scope(op="mixer_add"):
                 kernels.residual_inject(resid, delta)
         if adds and getattr(self.ff, "can_add_into", False):
-            return self.ff.forward(xn, batch, add_into=resid)
-        return self.ff.forward(xn, batch)
+            return self.ff.forward(xf, batch, add_into=resid)
+        return self.ff.forward(xf, batch)
+
+
+@register_arrangement("parallel_two_norms")
+class ParallelTwoNormsBlock(ParallelBlock):
+    """x += mixer(norm1(x)) + ff(norm2(x)): the parallel layer with a norm for each sublayer, both of the same x.
+
+    Two norms of one row with one eps share the row's statistics and differ by their weights, so one kernel adds
+    what the layer before left pending, and writes both sublayers' inputs.  Everything else is the parallel layer."""
+
+    def __init__(self, spec: LayerSpec, hidden: int, env: BuildEnv, mixer_spec=None):
+        super().__init__(spec, hidden, env, mixer_spec)
+        self.ff_norm = build_norm(spec.ff_norm, hidden, env) if self.ff is not None else None
+
+    def _parts(self):
+        out = super()._parts()
+        if self.ff_norm is not None:
+            out.insert(1, (self.ff_norm, f"{self.prefix}.{self.spec.ff_norm_name}"))
+        return out
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        return super().workspace_bytes(n_tokens) + (self.ff_norm.workspace_bytes(n_tokens) if self.ff_norm is not None else 0)
+
+    def _normed(self, resid, pending, T):
+        if self.ff_norm is None:
+            return super()._normed(resid, pending, T)
+        with scope(op="mixer_norm"):
+            if hasattr(self.norm, "forward_with"):
+                return self.norm.forward_with(self.ff_norm, resid, pending, T)
+            xn = self.norm.forward(resid, pending, T)
+            if isinstance(xn, DeferredNorm):
+                xn = xn.materialize()
+            return xn, self.ff_norm.forward(resid, None, T)

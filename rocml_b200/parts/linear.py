@@ -52,10 +52,17 @@ def _labelled(fn):
 
 
 class Linear:
-    def __init__(self, names: Sequence[str], out_features: Sequence[int], in_features: int, bias: bool,
+    def __init__(self, names: Sequence[str], out_features: Sequence[int], in_features: int, bias,
                  env: BuildEnv):
-        """``names`` are the tensor-name stems stacked along out (e.g. q_proj, k_proj, v_proj)."""
+        """``names`` are the tensor-name stems stacked along out (e.g. q_proj, k_proj, v_proj).  ``bias``: whether
+        they have biases, all of them (True) or those of the stems it lists (the others' part of the stacked
+        bias is zero)."""
         self.names = list(names)
+        if not isinstance(bias, bool):
+            self.biased = [n for n in self.names if n in set(bias)]
+            bias = bool(self.biased)
+        else:
+            self.biased = list(self.names) if bias else []
         self.label = "+".join(n.rsplit(".", 1)[-1] for n in self.names)
         self.outs = list(out_features)
         self.n = sum(self.outs)
@@ -70,7 +77,7 @@ class Linear:
         out = []
         for name, n in zip(self.names, self.outs):
             out.append(TensorDecl(f"{prefix}{name}.weight", (n, self.k), "matrix"))
-            if self.has_bias:
+            if name in self.biased:
                 out.append(TensorDecl(f"{prefix}{name}.bias", (n,), "bias"))
         return out
 
@@ -80,7 +87,9 @@ class Linear:
             ws = [w.float() for w in ws]  # stacked parts stored in different types: widen all
         self.weight = ws[0] if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
         if self.has_bias:
-            self.bias = torch.cat([tensors[f"{prefix}{n}.bias"].float() for n in self.names]).contiguous()
+            self.bias = torch.cat([tensors[f"{prefix}{n}.bias"].float() if n in self.biased else
+                                   torch.zeros(k, dtype=torch.float32, device=self.weight.device)
+                                   for n, k in zip(self.names, self.outs)]).contiguous()
 
     def pad_rows(self, multiple: int) -> None:
         """Append zero rows to the loaded weight until its row count is a multiple of ``multiple``: a stack of

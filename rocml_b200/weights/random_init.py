@@ -2,7 +2,8 @@
 
 The reference has no such mode (it always opens a checkpoint); benchmarks and
 tests here need one because no checkpoint can be fetched.  Distributions: linear
-weights and embeddings N(0, 0.02); norm scales 1 + N(0, 0.1); biases N(0, 0.02).
+weights and embeddings N(0, 0.02); norm scales 1 + N(0, 0.1); biases N(0, 0.02); a fraction
+(a blend's share) 0.5 + N(0, 0.15).
 Each tensor's values depend only on (seed, tensor name), never on the order in
 which tensors are produced, and are rounded to bfloat16 so that the 32-bit and
 the bfloat16 paths see exactly the same numbers.
@@ -33,6 +34,8 @@ def random_tensor(decl: TensorDecl, seed: int, device="cpu", dtype=torch.bfloat1
     x = torch.randn(decl.shape, generator=g, device=device, dtype=torch.float32)
     if decl.role == "norm":
         x.mul_(0.1).add_(1.0)
+    elif decl.role == "fraction":
+        x.mul_(0.15).add_(0.5)
     else:
         x.mul_(0.02)
     return x.to(dtype)

@@ -224,7 +224,7 @@ def write_safetensors(path: str, layout: Iterable[Tuple[str, torch.dtype, Tuple[
                     f"writer: expected {name} {dtype} {list(shape)}, got {got_name} {t.dtype} {list(t.shape)}"
                 )
             t = t.detach().cpu().contiguous()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")
     os.replace(tmp, path)
 
 

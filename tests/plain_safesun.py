@@ -117,7 +117,8 @@ def attention(h, w, pre, kind, m, eps, v_first=None, positions=None):
     v_own = v
     if v_first is not None:
         v = mix_values(v, v_first, w[pre + "vmix"])
-    seen = visible(pos, m["mask"]["size"], m["mask"]["keep_first"])
+    mask = m.get("mask") or {"size": T + max(pos) + 1, "keep_first": 0}        # no mask: every earlier key
+    seen = visible(pos, mask["size"], mask.get("keep_first", 0))
     out = torch.empty((T, H, vdim), dtype=h.dtype)
     for n in range(H):
         g = n // (H // G)

@@ -248,3 +248,71 @@ def write_zokelorn(folder, cfg_dict, seed, std=0.05, sharp=1.0, router_gain=3.0,
         w[k] = t.to(torch.bfloat16)
     save_file(w, path)
     return folder
+
+
+# ---- Safesun: small configurations that differ in every size, option and constant -------------------------------
+def _sattn(kind, heads, kv, dim, vdim, scale, mask, rot, v_mix):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale, "v_mix": v_mix}
+    if mask is not None:
+        m["mask"] = {"size": mask[0], "keep_first": mask[1]}
+    if rot is not None:
+        m["rot"] = {"base": rot[0], "dims": rot[1]}
+        if len(rot) > 2:
+            m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), rot[2]))
+    return {"type": kind, "mixer": m}
+
+
+def _s(layer, ff):
+    return {**layer, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+# SA: value heads narrower and wider than key heads, two key/value heads, rotation of half, a third and all of a head,
+# frequencies blended along a ramp, a window shorter than the kept first positions (which cross a page border), a layer
+# without feed-forward, a layer that takes no part in the blending of values between two that do
+SAFESUN_A = {
+    "architecture": "Safesun", "vocab": 211, "width": 64, "norm": {"eps": 1e-6},
+    "layers": [_s(_sattn("attention_2", 4, 2, 32, 16, 0.3, (37, 5), (10000.0, 16), True), 96),
+               _s(_sattn("attention", 4, 2, 16, 16, 0.6, (70, 0), (1000.0, 16, (4.0, 64, 8.0, 1.0)), True), None),
+               _s(_sattn("attention", 3, 1, 24, 40, 0.45, (9, 70), (200.0, 8), False), 52),
+               _s(_sattn("attention_2", 2, 2, 16, 16, 0.7, (300, 1), (50000.0, 16, (2.5, 32, 4.0, 0.5)), True), 40)],
+}
+# SB: head sizes 64 and 128 (which the bfloat16 attention kernels take), eight query heads a key/value head, a window
+# and kept positions of exactly one page, a window of one position, kept positions as long as the window
+SAFESUN_B = {
+    "architecture": "Safesun", "vocab": 333, "width": 128, "norm": {"eps": 1e-5},
+    "layers": [_s(_sattn("attention", 8, 1, 64, 64, 0.2, (64, 64), (1000000.0, 64), False), 160),
+               _s(_sattn("attention_2", 4, 2, 128, 128, 0.08, (150, 3), (30000.0, 32, (8.0, 128, 16.0, 2.0)), True), 64),
+               _s(_sattn("attention_2", 8, 2, 64, 128, 0.15, (1, 0), (500.0, 64), True), None),
+               _s(_sattn("attention", 2, 2, 128, 128, 0.1, (130, 130), (7000.0, 128, (3.0, 200, 20.0, 1.5)), True), 96)],
+}
+# SC: sizes that are multiples of four only, head sizes that are no multiple of 16, as many key/value heads as query
+# heads, no rotation, a layer that sees every earlier key, a single layer that would blend values (so none does),
+# more query heads a key/value head than one block of the decode kernel takes
+SAFESUN_C = {
+    "architecture": "Safesun", "vocab": 97, "width": 72, "norm": {"eps": 3e-5},
+    "layers": [_s(_sattn("attention", 3, 3, 20, 28, 0.5, (1, 1), None, False), None),
+               _s(_sattn("attention_2", 6, 1, 12, 12, 0.9, None, (100.0, 12), True), 52),
+               _s(_sattn("attention_2", 20, 1, 16, 16, 0.55, (90, 33), (10000.0, 4), False), 28)],
+}
+SAFESUN = {"SA": SAFESUN_A, "SB": SAFESUN_B, "SC": SAFESUN_C}
+
+
+def write_safesun(folder, cfg_dict, seed, std=0.06):
+    """A Safesun model folder with random weights: matrices of standard deviation ``std``, the stream's norm weights
+    around zero (they act as 1 + w), the per-head norm weights around one, biases large enough to matter, the blend's
+    shares between a quarter and three quarters."""
+    from safetensors.torch import load_file, save_file
+    write_model(folder, cfg_dict, seed)
+    path = os.path.join(folder, "model.safetensors")
+    w = load_file(path)
+    for k in sorted(w):
+        t = w[k].float()
+        if t.dim() == 2:
+            t = t * (std / 0.02)
+        elif k.endswith((".norm1", ".norm2")) or k in ("embed.norm", "final.norm"):
+            t = (t - 1.0) * 2.0
+        elif k.endswith(".b"):
+            t = t * 10.0
+        w[k] = t.to(torch.bfloat16)
+    save_file(w, path)
+    return folder

@@ -166,13 +166,25 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     return d;
 }
 
+// A row's result from its accumulated values A, sum L and maximum M (in powers of two: scores carry the factor
+// log2 e); with a sink score the denominator has the term e^sink as well.
+__device__ __forceinline__ float finished(float A, float L, float M, float sink) {
+    if (has_sink(sink)) {
+        const float s2 = sink * LOG2E, m2 = fmaxf(M, s2);
+        const float a = exp2f(M - m2);
+        L = L * a + exp2f(s2 - m2);
+        A *= a;
+    }
+    return L > 0.f ? A / L : 0.f;
+}
+
 template <int HD, bool CL, bool FQ, bool PROP, bool TR>
 __global__ void __launch_bounds__(WARPS * 32, HD <= 128 ? 3 : 1)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slot,
                         const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
-                        float scale, int window, int n_chunks, int ppb, float* __restrict__ part_acc,
+                        float scale, int window, int keep, float sink, int n_chunks, int ppb, float* __restrict__ part_acc,
                         float* __restrict__ part_ml, int* __restrict__ counters,
                         __nv_bfloat16* __restrict__ out, int o_stride, const Projections pj, int n_seqs) {
     pdl_trigger();
@@ -251,7 +263,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         if (!CL && page_first * CHUNK > pos) return;
         page_last = min(pos / CHUNK, page_first + ppb - 1);
         parts_hi = pos / (CHUNK * ppb);
-        parts_lo = win_lo / (CHUNK * ppb);
+        parts_lo = keep > 0 ? 0 : win_lo / (CHUNK * ppb);    // kept first keys: the parts between them and the window are empty
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -264,7 +276,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     auto issue = [&](int page_idx, int buf) {
         const int j0 = page_idx * CHUNK + warp * WK;
         const int hi = min(pos, (page_idx + 1) * CHUNK - 1);
-        const bool any = page_idx <= page_last && j0 <= hi && j0 + WK - 1 >= win_lo;
+        const bool any = page_idx <= page_last && j0 <= hi && (j0 + WK - 1 >= win_lo || j0 < keep);
         if (any) {
             const int page = table[page_idx];
             const size_t off = (((size_t)(page < 0 ? 0 : page) * nkv + kvh) * RB_PAGE + warp * WK) * HD;
@@ -358,7 +370,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     auto attend_page = [&](int pg, int buf) {
         const int j0 = pg * CHUNK + warp * WK;
         const int hi = min(pos, (pg + 1) * CHUNK - 1);
-        if (!(j0 <= hi && j0 + WK - 1 >= win_lo)) return;
+        if (!(j0 <= hi && (j0 + WK - 1 >= win_lo || j0 < keep))) return;
+        const bool whole = (j0 >= win_lo || j0 + WK <= keep) && j0 + WK - 1 <= hi;     // no key of the slice is masked
         const uint32_t ks_base = smem_addr(KVw + buf * 2 * WK * HD);
         const uint32_t vs_base = ks_base + WK * HD * 2;
         if constexpr (TR) {
@@ -374,11 +387,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 mma_bf16(st2, kb, qb[ks + 1][0], qb[ks + 1][1]);
             }
             const int key0 = j0 + gq, key1 = key0 + 8;
-            if (j0 >= win_lo && j0 + WK - 1 <= hi) {
+            if (whole) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) st[e] = (st[e] + st2[e]) * sl2;
             } else {
-                const bool ok0 = key0 >= win_lo && key0 <= hi, ok1 = key1 >= win_lo && key1 <= hi;
+                const bool ok0 = (key0 >= win_lo || key0 < keep) && key0 <= hi, ok1 = (key1 >= win_lo || key1 < keep) && key1 <= hi;
                 st[0] = ok0 ? (st[0] + st2[0]) * sl2 : -INFINITY;
                 st[1] = ok0 ? (st[1] + st2[1]) * sl2 : -INFINITY;
                 st[2] = ok1 ? (st[2] + st2[2]) * sl2 : -INFINITY;
@@ -442,7 +455,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         // every row is the same token, so one mask serves all rows) and the rescaling of the output
         // (the running maximum seldom moves after the first pages).
         float mx[2] = {NEG_BIG, NEG_BIG};
-        if (j0 >= win_lo && j0 + WK - 1 <= hi) {
+        if (whole) {
 #pragma unroll
             for (int j = 0; j < WK / 8; ++j) {
 #pragma unroll
@@ -456,7 +469,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int key = j0 + j * 8 + tq * 2 + (e & 1);
-                    const bool ok = key >= win_lo && key <= hi;
+                    const bool ok = (key >= win_lo || key < keep) && key <= hi;
                     s[j][e] = ok ? s[j][e] * sl2 : -INFINITY;
                 }
                 mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
@@ -577,7 +590,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             part_acc[pidx * HD + d] = A;
             if (d == 0) { part_ml[pidx * 2] = M; part_ml[pidx * 2 + 1] = L; }
         } else {
-            out[(size_t)t * o_stride + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+            out[(size_t)t * o_stride + (size_t)head * HD + d] = __float2bfloat16_rn(finished(A, L, M, sink));
         }
     }
     if (CL) {
@@ -615,7 +628,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                     A = fmaf(wt, pa[i], A);
                 }
             }
-            out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+            out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(finished(A, L, MM, sink));
         }
         cluster_sync_all();                                  // nobody leaves while its part may still be read
         return;
@@ -664,7 +677,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             L = fmaf(wt, pl[i], L);
             A = fmaf(wt, __ldcg(pa + (size_t)i * HD), A);
         }
-        out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+        out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(finished(A, L, MM, sink));
     }
    }
 round_done:
@@ -684,8 +697,8 @@ bool cluster_enabled() {
 template <int HD, bool CL, bool FQ, bool PROP, bool TR>
 int launch_variant(dim3 grid, size_t smem, cudaStream_t s, const void* q, int q_stride, const void* k_cache,
                    const void* v_cache, const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
-                   const int* kv_len, int nq, int nkv, float scale, int window, int n_chunks, int ppb, float* part_acc,
-                   float* part_ml, int* counters, void* out, int o_stride, const Projections& pj, int n_seqs) {
+                   const int* kv_len, int nq, int nkv, float scale, int window, int keep, float sink, int n_chunks, int ppb,
+                   float* part_acc, float* part_ml, int* counters, void* out, int o_stride, const Projections& pj, int n_seqs) {
     auto k = attention_decode_kernel<HD, CL, FQ, PROP, TR>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -700,12 +713,12 @@ int launch_variant(dim3 grid, size_t smem, cudaStream_t s, const void* q, int q_
     if (CL) {
         cudaError_t e = launch_clustered(k, grid, dim3(WARPS * 32), dim3(grid.x, 1, 1), smem, s, (const __nv_bfloat16*)q,
                                          q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-                                         block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
+                                         block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, keep, sink,
                                          n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride, pj, n_seqs);
         return e == cudaSuccess ? RB_OK : (int)e;
     } else {
         RB_LAUNCH((k), grid, dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
-                  (const __nv_bfloat16*)v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
+                  (const __nv_bfloat16*)v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, keep, sink,
                   n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride, pj, n_seqs);
         return RB_OK;
     }
@@ -714,11 +727,13 @@ int launch_variant(dim3 grid, size_t smem, cudaStream_t s, const void* q, int q_
 template <int HD>
 int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
            int max_pages, const int* seq_slot, const int* cu_q, const int* kv_len, int B, int nq, int nkv,
-           float scale, int window, int n_chunks, int ppb, float* part_acc, float* part_ml, int* counters,
-           void* out, int o_stride, const Projections& pj, cudaStream_t s) {
+           float scale, int window, int keep, float sink, int n_chunks, int ppb, float* part_acc, float* part_ml,
+           int* counters, void* out, int o_stride, const Projections& pj, cudaStream_t s) {
     const int g = nq / nkv;
     const bool proportional = ppb == 0;     // n_chunks blocks a head group share the pages of all sequences equally
     if (proportional && B > PROP_MAX_SEQS) return RB_ERR_BAD_SIZE;
+    // the equal shares count a sequence's pages from its window's first; kept first keys are pages apart from those
+    if (keep < 0 || (keep > 0 && (proportional || window < 0))) return RB_ERR_BAD_SIZE;
     dim3 grid(n_chunks, nkv * ((g + ROWS - 1) / ROWS), proportional ? 1 : B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
     const size_t kv_bytes = (size_t)WARPS * 4 * WK * HD * sizeof(__nv_bfloat16);   // two buffers per warp
@@ -737,10 +752,10 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     if (fused && pj.write_kv && g > ROWS) return RB_ERR_BAD_SIZE;
     // groups of up to 8 heads (every size of the architecture): the transposed products (see the kernel)
 #define RB_ADV(CL, FQ, PROP) (g <= 8 ? launch_variant<HD, CL, FQ, PROP, true>(grid, smem, s, q, q_stride, k_cache, v_cache, block_table, \
-                                                         max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,         \
+                                                         max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, keep, sink, \
                                                          n_chunks, ppb, part_acc, part_ml, counters, out, o_stride, pj, B)  \
                                      : launch_variant<HD, CL, FQ, PROP, false>(grid, smem, s, q, q_stride, k_cache, v_cache, block_table, \
-                                                         max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,         \
+                                                         max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, keep, sink, \
                                                          n_chunks, ppb, part_acc, part_ml, counters, out, o_stride, pj, B))
     if (proportional) return (HD == 128 && fused) ? RB_ADV(false, (HD == 128), true) : RB_ADV(false, false, true);
     if (HD == 128 && fused) return clustered ? RB_ADV(true, (HD == 128), false) : RB_ADV(false, (HD == 128), false);
@@ -762,7 +777,7 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
 // uses the plain kernel.
 static int decode_entry(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                         const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
-                        const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
+                        const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window, int keep, float sink,
                         int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
                         int* counters, void* out, int o_stride, const Projections& pj, void* stream) {
     if (B <= 0) return RB_OK;
@@ -772,7 +787,7 @@ static int decode_entry(const void* q, int q_stride, const void* k_cache, const 
     if (pj.proj == nullptr && (((uintptr_t)q & 15) || (q_stride % 8))) return RB_ERR_BAD_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
 #define RB_AD(HD) return launch<HD>(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, \
-                                    nkv, scale, window, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, pj, s)
+                                    nkv, scale, window, keep, sink, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, pj, s)
     if (hd == 128) RB_AD(128);
     if (hd == 64) RB_AD(64);
     if (hd == 256) RB_AD(256);
@@ -783,11 +798,11 @@ static int decode_entry(const void* q, int q_stride, const void* k_cache, const 
 extern "C" int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                    const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                                    const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
-                                   int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
+                                   int keep, float sink, int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
                                    int* counters, void* out, int o_stride, void* stream) {
     Projections none = {};
     return decode_entry(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, nkv, hd,
-                        scale, window, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, none, stream);
+                        scale, window, keep, sink, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, none, stream);
 }
 
 // The same for head size 128 with the step's projections as the matrix product left them:
@@ -822,7 +837,7 @@ extern "C" int rb_attention_decode_fused(const float* proj, int n_in, long long 
     pj.row_eps = row_eps; pj.row_inv_width = row_width > 0 ? 1.f / (float)row_width : 0.f;
     if (row_sumsq != nullptr && (row_groups < 1 || row_width < 1)) return RB_ERR_BAD_SIZE;
     return decode_entry(nullptr, 0, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, nkv, hd,
-                        scale, window, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, pj, stream);
+                        scale, window, 0, RB_NO_SINK, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, pj, stream);
 }
 
 // ---- the same kernel for callers that cannot allocate (see no_alloc.h) -----------------------------
@@ -889,6 +904,6 @@ extern "C" int rb_attention_decode_static(const void* q, int q_stride, const voi
     cudaError_t e = cudaMemsetAsync(sc->counters, 0, n_counters * sizeof(int), (cudaStream_t)stream);
     if (e != cudaSuccess) return (int)e;
     return rb_attention_decode(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, n_seqs,
-                               nq, nkv, hd, scale, window, n_chunks, 1, sc->acc, sc->ml, sc->counters, out, o_stride,
+                               nq, nkv, hd, scale, window, 0, RB_NO_SINK, n_chunks, 1, sc->acc, sc->ml, sc->counters, out, o_stride,
                                stream);
 }

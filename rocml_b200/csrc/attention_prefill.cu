@@ -6,7 +6,9 @@
 // contiguous at a head size of 128), double-buffered in shared memory with cp.async.  Shared-memory
 // rows are stored with their 16-byte chunks XOR-swizzled by the row number so that ldmatrix reads
 // are free of bank conflicts.  Per tile: S = Q K^T, scale, mask (causal, inclusive; window; end of
-// the sequence), online softmax in float32, P (rounded to bfloat16) times V.  The query's position
+// the sequence; beside a window the first `keep` positions may stay visible: their tiles are visited
+// first and the tiles between them and the window are skipped), online softmax in float32 (with one more
+// term exp(sink) in the denominator when the layer has one), P (rounded to bfloat16) times V.  The query's position
 // is its absolute position in its sequence, so a piece of a prompt attends to the cache that
 // earlier steps left.
 //
@@ -34,7 +36,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          int o_stride, const __nv_bfloat16* __restrict__ k_cache,
                          const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                          int max_pages, const int* __restrict__ seq_slot, const int* __restrict__ cu_q,
-                         const int* __restrict__ kv_len, int nq, int nkv, float scale, int window) {
+                         const int* __restrict__ kv_len, int nq, int nkv, float scale, int window, int keep,
+                         float sink) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -55,6 +58,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const int hi = pos0 + m0 + rows_here - 1;           // last key any row of the block may see
     const int lo = span_lo(pos0 + m0, window);
     const int kt_first = lo / BN, kt_last = hi / BN;
+    // kept first keys: their tiles come before the window's, the tiles in between are skipped
+    const int kept_tiles = keep > 0 ? min((keep + BN - 1) / BN, kt_first) : 0;
+    const int n_tiles = kept_tiles + kt_last - kt_first + 1;
+    auto tile_of = [&](int j) { return j < kept_tiles ? j : kt_first + (j - kept_tiles); };
     const int* table = block_table + (size_t)slot * max_pages;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -70,7 +77,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
 
     load_tile<HD>(Qs, q + (size_t)(q0 + m0) * q_stride + (size_t)head * HD, q_stride, BM, rows_here, threadIdx.x,
                   NWARPS * 32);
-    load_kv(kt_first, 0);
+    load_kv(tile_of(0), 0);
     cp_async_commit();
 
     // this warp's rows: m0 + warp*16 + g and + 8
@@ -83,13 +90,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const float sl2 = scale * LOG2E;
     const uint32_t qs_base = smem_addr(Qs);
 
-    for (int kt = kt_first; kt <= kt_last; ++kt) {
-        const int buf = (kt - kt_first) & 1;
+    for (int j = 0; j < n_tiles; ++j) {
+        const int kt = tile_of(j);
+        const int buf = j & 1;
         cp_async_wait<0>();
         __syncthreads();                                  // tile kt has landed; the other buffer is free
-        if (kt + 1 <= kt_last) load_kv(kt + 1, buf ^ 1);
+        if (j + 1 < n_tiles) load_kv(tile_of(j + 1), buf ^ 1);
         cp_async_commit();
-        if (kt == kt_first) {
+        if (j == 0) {
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
                 const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -121,7 +129,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
             for (int e = 0; e < 4; ++e) {
                 const int key = kt * BN + j * 8 + t * 2 + (e & 1);
                 const int r = e >> 1;
-                const bool ok = key <= row_pos[r] && key >= span_lo(row_pos[r], window);
+                const bool ok = key <= row_pos[r] && (key >= span_lo(row_pos[r], window) || key < keep);
                 s[j][e] = ok ? s[j][e] * sl2 : -INFINITY;
                 mx[r] = fmaxf(mx[r], s[j][e]);
             }
@@ -172,6 +180,21 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
+    if (has_sink(sink)) {                                // one more term in every row's denominator
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const float s2 = sink * LOG2E, m2 = fmaxf(m_run[r], s2);
+            const float a = exp2f(m_run[r] - m2);
+            l_run[r] = l_run[r] * a + exp2f(s2 - m2);
+            if (r == 0) {
+#pragma unroll
+                for (int i = 0; i < HD / 8; ++i) { o[i][0] *= a; o[i][1] *= a; }
+            } else {
+#pragma unroll
+                for (int i = 0; i < HD / 8; ++i) { o[i][2] *= a; o[i][3] *= a; }
+            }
+        }
+    }
     const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
     const float inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
     const int r0 = m0 + warp * 16 + g, r1 = r0 + 8;
@@ -190,7 +213,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
 template <int HD>
 int launch(const void* q, int q_stride, void* out, int o_stride, const void* k_cache, const void* v_cache,
            const int* block_table, int max_pages, const int* seq_slot, const int* cu_q, const int* kv_len, int B,
-           int max_q_len, int nq, int nkv, float scale, int window, cudaStream_t s) {
+           int max_q_len, int nq, int nkv, float scale, int window, int keep, float sink, cudaStream_t s) {
     const size_t smem = (size_t)(BM + 4 * BN) * HD * sizeof(__nv_bfloat16);
     auto k = attention_prefill_kernel<HD>;
     static bool attr_done = false;
@@ -203,26 +226,29 @@ int launch(const void* q, int q_stride, void* out, int o_stride, const void* k_c
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((k), grid, dim3(NWARPS * 32), smem, s, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
               o_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table, max_pages,
-              seq_slot, cu_q, kv_len, nq, nkv, scale, window);
+              seq_slot, cu_q, kv_len, nq, nkv, scale, window, keep, sink);
     return RB_OK;
 }
 }  // namespace
 
-// q rows [T, >= nq*hd] bfloat16 -> out rows; keys and values from the pages.  Returns
+// q rows [T, >= nq*hd] bfloat16 -> out rows; keys and values from the pages.  keep: beside a window the keys at
+// positions below it stay visible; sink: a score whose exponential joins every row's denominator (RB_NO_SINK: none).  Returns
 // RB_ERR_BAD_SIZE for head sizes other than 64, 128, 256 and RB_ERR_BAD_ALIGN for rows or pointers
 // off a 16-byte boundary (the caller then uses the plain kernel).
 extern "C" int rb_attention_prefill(const void* q, int q_stride, void* out, int o_stride, const void* k_cache,
                                     const void* v_cache, const int* block_table, int max_pages,
                                     const int* seq_slot, const int* cu_q, const int* kv_len, int B, int max_q_len,
-                                    int nq, int nkv, int hd, float scale, int window, void* stream) {
+                                    int nq, int nkv, int hd, float scale, int window, int keep, float sink,
+                                    void* stream) {
     if (B <= 0 || max_q_len <= 0) return RB_OK;
-    if (nkv <= 0 || nq % nkv) return RB_ERR_BAD_SIZE;
+    if (nkv <= 0 || nq % nkv || keep < 0) return RB_ERR_BAD_SIZE;
+    if (window <= 0) keep = 0;                            // kept first keys stand beside a window only
     if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 3) ||
         (q_stride % 8) || (o_stride % 2))
         return RB_ERR_BAD_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
 #define RB_AP(HD) return launch<HD>(q, q_stride, out, o_stride, k_cache, v_cache, block_table, max_pages, seq_slot, \
-                                    cu_q, kv_len, B, max_q_len, nq, nkv, scale, window, s)
+                                    cu_q, kv_len, B, max_q_len, nq, nkv, scale, window, keep, sink, s)
     if (hd == 128) RB_AP(128);
     if (hd == 64) RB_AP(64);
     if (hd == 256) RB_AP(256);

@@ -9,7 +9,8 @@
 // the MMAs, warps 2-5 are the 128 softmax threads.
 // Per tile: S_j = Q K_j^T into one of two TMEM buffers (so the tensor core can already form S_{j+1}
 // while the softmax works on S_j); the softmax threads read their row, mask (causal, inclusive;
-// window), update the running maximum and sum in float32 (base 2, the scale folded into the
+// window, beside which the first `keep` positions may stay visible: their tiles are walked first and the
+// tiles between them and the window are skipped), update the running maximum and sum in float32 (base 2, the scale folded into the
 // exponent's multiply-add, two scores an instruction), and write P as pairs of bfloat16 back into
 // the first 32 columns of the buffer S_j came from: the tensor core reads its A operand from there
 // (no shared-memory round trip, no proxy fence; S_{j+2} is issued into that buffer after the product
@@ -114,7 +115,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int o_stride,
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slot,
                              const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
-                             float scale, int window, int heads_first, int strict_order, int* __restrict__ status) {
+                             float scale, int window, int keep, float sink, int heads_first, int strict_order,
+                             int* __restrict__ status) {
     using Z = Sizes<HD>;
     constexpr int HALVES = Z::HALVES, Q_BYTES = Z::Q_BYTES, KV_TILE = Z::KV_TILE, Q_HALF = Z::Q_HALF, KV_HALF = Z::KV_HALF;
     constexpr int TILE_BYTES = Z::TILE_BYTES, SMEM_BYTES = Z::SMEM_BYTES, TMEM_COLS = Z::TMEM_COLS;
@@ -149,7 +151,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int hi = pos0 + m0 + rows_here - 1;
     const int lo = rb::span_lo(pos0 + m0, window);
     const int kt_first = lo / BNK, kt_last = hi / BNK;
-    const int n_tiles = kt_last - kt_first + 1;
+    // kept first keys: their tiles come before the window's, the tiles in between are skipped
+    const int kept_tiles = keep > 0 ? min((keep + BNK - 1) / BNK, kt_first) : 0;
+    const int n_tiles = kept_tiles + kt_last - kt_first + 1;
+    auto tile_of = [&](int j) { return j < kept_tiles ? j : kt_first + (j - kept_tiles); };
     const int* table = block_table + (size_t)slot * max_pages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -185,7 +190,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             for (int h = 0; h < HALVES; ++h) tma_load_2d(Qs + h * Q_HALF, &map_q, head * HD + h * 64, q0 + m0, &bar->q_full);
             bool ok = true;
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int page = table[kt_first + j];
+                const int page = table[tile_of(j)];
                 const int row = ((page < 0 ? 0 : page) * nkv + kvh) * RB_PAGE;
                 const int s = j & 1;
                 ok = mbar_wait(&bar->k_empty[s], ((j >> 1) & 1) ^ 1);
@@ -275,7 +280,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             alive = __all_sync(0xffffffffu, wait_or_abort(&bar->s_full[s], (j >> 1) & 1, &bar->abort_flag));
             if (!alive) break;
             tc_fence_after();
-            const int key0 = (kt_first + j) * BNK;
+            const int key0 = tile_of(j) * BNK;
             float sv[BNK];
             static_assert(BNK == 64, "one load of 64 columns");
             tmem_ld64(lane_base + s * BNK, sv);
@@ -285,11 +290,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             // special-function instruction for 2^x.
             // a tile that every row of this warp sees whole needs no mask
             const int warp_first_pos = pos0 + m0 + quarter * 32;
-            if (!(key0 + BNK - 1 <= warp_first_pos && key0 >= rb::span_lo(warp_first_pos + 31, window))) {
+            if (!(key0 + BNK - 1 <= warp_first_pos && (key0 >= rb::span_lo(warp_first_pos + 31, window) || key0 + BNK <= keep))) {
 #pragma unroll
                 for (int i = 0; i < BNK; ++i) {
                     const int key = key0 + i;
-                    const bool ok = key <= row_pos && key >= rb::span_lo(row_pos, window);
+                    const bool ok = key <= row_pos && (key >= rb::span_lo(row_pos, window) || key < keep);
                     sv[i] = ok ? sv[i] : -INFINITY;
                 }
             }
@@ -373,6 +378,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         if (alive) alive = __all_sync(0xffffffffu, wait_or_abort(&bar->o_final, 0, &bar->abort_flag));
         if (alive) {
             tc_fence_after();
+            // one more term in the denominator: O and the sum carry the factor 2^-m_used, so the term does too
+            if (rb::has_sink(sink)) l_sum += exp2f(fminf(sink * LOG2E - m_used, 126.f));
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             __nv_bfloat16* orow = out + (size_t)(q0 + m0 + r) * o_stride + (size_t)head * HD;
 #pragma unroll 1
@@ -456,8 +463,8 @@ int make_map(const void* ptr, long long rows, long long cols, long long ld, int 
 template <int HD>
 int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, const void* k_cache, const void* v_cache,
                int n_pages, const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
-               const int* kv_len, int B, int max_q_len, int nq, int nkv, float scale, int window, int heads_first,
-               int* status, cudaStream_t stream) {
+               const int* kv_len, int B, int max_q_len, int nq, int nkv, float scale, int window, int keep, float sink,
+               int heads_first, int* status, cudaStream_t stream) {
     // RB_PREFILL_STRICT_ORDER=0: see `strict_order` in the kernel's MMA thread
     static const int strict_order = [] { const char* e = getenv("RB_PREFILL_STRICT_ORDER"); return (e && e[0] == '0') ? 0 : 1; }();
     CUtensorMap mq, mk, mv;
@@ -477,26 +484,30 @@ int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, cons
     dim3 grid = heads_first ? dim3(nq, B, q_tiles) : dim3(q_tiles, nq, B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((k), grid, dim3(192), Sizes<HD>::SMEM_BYTES, stream, mq, mk, mv, (__nv_bfloat16*)out, o_stride,
-              block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, heads_first, strict_order, status);
+              block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, keep, sink, heads_first, strict_order,
+              status);
     return RB_OK;
 }
 }  // namespace
 
 // q rows [T, q_stride] bfloat16 (T = tokens of the step), caches [n_pages, nkv, 64, hd].  heads_first: the order
-// in which blocks start (see the kernel); it changes no result.  Head sizes 64, 128 and 256;
+// in which blocks start (see the kernel); it changes no result.  keep: beside a window the keys at positions below
+// it stay visible; sink: a score whose exponential joins every row's denominator (RB_NO_SINK: none).  Head sizes 64, 128 and 256;
 // RB_ERR_BAD_SIZE / RB_ERR_BAD_ALIGN otherwise (the caller then uses the mma.sync kernel).
 extern "C" int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void* out, int o_stride,
                                         const void* k_cache, const void* v_cache, int n_pages,
                                         const int* block_table, int max_pages, const int* seq_slot,
                                         const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv,
-                                        int hd, float scale, int window, int heads_first, int* status, void* stream) {
+                                        int hd, float scale, int window, int keep, float sink, int heads_first,
+                                        int* status, void* stream) {
     if (B <= 0 || max_q_len <= 0 || T <= 0) return RB_OK;
-    if ((hd != 64 && hd != 128 && hd != 256) || nkv <= 0 || nq % nkv) return RB_ERR_BAD_SIZE;
+    if ((hd != 64 && hd != 128 && hd != 256) || nkv <= 0 || nq % nkv || keep < 0) return RB_ERR_BAD_SIZE;
+    if (window <= 0) keep = 0;                            // kept first keys stand beside a window only
     if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15) ||
         (q_stride % 8) || (o_stride % 8))
         return RB_ERR_BAD_ALIGN;
 #define RB_TC5_ARGS q, q_stride, T, out, o_stride, k_cache, v_cache, n_pages, block_table, max_pages, seq_slot, cu_q, kv_len, \
-                    B, max_q_len, nq, nkv, scale, window, heads_first, status, (cudaStream_t)stream
+                    B, max_q_len, nq, nkv, scale, window, keep, sink, heads_first, status, (cudaStream_t)stream
     if (hd == 64) return launch_tc5<64>(RB_TC5_ARGS);
     if (hd == 128) return launch_tc5<128>(RB_TC5_ARGS);
     return launch_tc5<256>(RB_TC5_ARGS);

@@ -139,10 +139,10 @@ def _lib():
         lib.rb_attention_merge.argtypes = [_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp]
         lib.rb_argmax.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _i, _vp]
         lib.rb_attention_prefill.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                                             _f, _i, _vp]
+                                             _f, _i, _i, _f, _vp]
         lib.rb_attention_prefill_tc5.argtypes = [_vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i,
-                                                 _i, _i, _i, _f, _i, _i, _vp, _vp]
-        lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
+                                                 _i, _i, _i, _f, _i, _i, _f, _i, _vp, _vp]
+        lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _f, _i,
                                             _i, _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_attention_decode_fused.argtypes = [_vp, _i, _ll, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _i, _ll, _f, _i,
                                                   _vp, _vp, _vp, _i, _vp, _vp,
@@ -421,8 +421,10 @@ def prefill_heads_first(n_seqs: int, nkv: int, hd: int, max_kv_len: int, window:
 def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                           block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                           n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
-                          max_kv_len: Optional[int] = None) -> bool:
+                          max_kv_len: Optional[int] = None, keep: int = 0, sink: Optional[float] = None) -> bool:
     """bfloat16 flash attention with tcgen05 (accumulators in tensor memory, TMA loads), head sizes 64, 128 and 256.
+    ``keep``: beside a window the keys at positions below it stay visible; ``sink``: a score whose exponential
+    joins every row's denominator.
     ``max_kv_len`` (the longest context of the step; the longest query if not given) only decides the
     order in which blocks start: the longest blocks of all heads first while the keys and values that
     the step reads fit the L2 cache, one head after another beyond.  Returns False when the kernel
@@ -435,7 +437,7 @@ def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_c
     rc = _lib().rb_attention_prefill_tc5(
         _ptr(q), q.stride(0), n_tokens, _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0],
         _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"),
-        _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window),
+        _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window), int(keep), _sink(sink),
         1 if prefill_heads_first(n_seqs, nkv, hd, max_q_len if max_kv_len is None else max_kv_len, window) else 0,
         _ptr(status_word(q.device)), _stream())
     if rc in (10001, 10003):
@@ -447,8 +449,11 @@ def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_c
 @_profiled(lambda a, facts: _attention_cost(a, facts))
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
-                      n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0) -> bool:
+                      n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
+                      keep: int = 0, sink: Optional[float] = None) -> bool:
     """bfloat16 flash attention on the tensor cores for any number of query tokens per sequence.
+    ``keep``: beside a window the keys at positions below it stay visible; ``sink``: a score whose exponential
+    joins every row's denominator.
     Returns False when the kernel does not take the head size or the alignment."""
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or \
             q.stride(-1) != 1 or out.stride(-1) != 1:
@@ -458,7 +463,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     rc = _lib().rb_attention_prefill(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"),
         block_table.shape[1], _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs,
-        max_q_len, nq, nkv, hd, float(scale), int(window), _stream())
+        max_q_len, nq, nkv, hd, float(scale), int(window), int(keep), _sink(sink), _stream())
     if rc in (10001, 10003):
         return False
     _check(rc, "attention_prefill")
@@ -527,8 +532,10 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                      block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                      n_seqs: int, nq: int, nkv: int, hd: int, scale: float, window: int, n_chunks: int,
                      part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
-                     pages_per_block: int = 1) -> bool:
-    """bfloat16 decode attention, one query token per sequence; a block takes ``pages_per_block``
+                     pages_per_block: int = 1, keep: int = 0, sink: Optional[float] = None) -> bool:
+    """``keep``: the keys at positions below it stay visible beside the window (not with ``pages_per_block`` 0);
+    ``sink``: a score whose exponential joins every row's denominator.
+    bfloat16 decode attention, one query token per sequence; a block takes ``pages_per_block``
     pages of 64 keys, ``n_chunks`` blocks cover the longest sequence and are merged by the kernel
     itself; part_acc / part_ml [T, nq, >= n_chunks, ...] are its work space when n_chunks > 1.
     ``pages_per_block`` 0: ``n_chunks`` blocks a key/value head group share the pages of all sequences
@@ -544,7 +551,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     rc = _lib().rb_attention_decode(
         _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"), block_table.shape[1],
         _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs, nq, nkv, hd, float(scale),
-        int(window), int(n_chunks), int(pages_per_block), _ptr(part_acc), _ptr(part_ml),
+        int(window), int(keep), _sink(sink), int(n_chunks), int(pages_per_block), _ptr(part_acc), _ptr(part_ml),
         _ptr(decode_counters(q.device)), _ptr(out),
         out.stride(0), _stream())
     if rc in (10001, 10003):

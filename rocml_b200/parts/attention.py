@@ -333,21 +333,25 @@ def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, s
     ``sink``: a score whose exponential joins every row's denominator.  One token per sequence:
     keys split in fixed chunks, partial results merged; otherwise whole rows.  Any mixer whose cache is
     such pages calls this (keys and values may be the same tensor)."""
-    special = bool(keep) or sink is not None      # what only the plain kernel takes so far
     if batch.is_decode:
         chunk = DECODE_CHUNK
         T = batch.n_tokens
         n_pages = max(1, (batch.max_kv_len + chunk - 1) // chunk)
         groups = nkv * ((nq // nkv + 15) // 16)
         n_blocks, ppb = kernels.decode_split(batch.n_seqs, groups, n_pages, q.device)
+        if keep and ppb == 0:
+            # equal shares of all sequences' pages count a sequence's pages from its window's first; with kept
+            # first keys a sequence takes whole blocks instead
+            ppb = -(-n_pages // min(n_pages, kernels.DECODE_CLUSTER_MAX))
+            n_blocks = -(-n_pages // ppb)
         acc = ml = None
         if n_pages > 1:
             parts = max(n_pages, n_blocks)
             acc = torch.empty((T, nq, parts, hd), dtype=torch.float32, device=q.device)
             ml = torch.empty((T, nq, parts, 2), dtype=torch.float32, device=q.device)
-        fast = not special and kernels.attention_decode(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
-                                                        batch.kv_len, batch.n_seqs, nq, nkv, hd, scale,
-                                                        window, n_blocks, acc, ml, ppb)
+        fast = kernels.attention_decode(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
+                                        batch.kv_len, batch.n_seqs, nq, nkv, hd, scale,
+                                        window, n_blocks, acc, ml, ppb, keep=keep, sink=sink)
         n_chunks = n_pages
         if fast:
             return
@@ -358,13 +362,13 @@ def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, s
             kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, nq, hd,
                                     chunk, n_chunks, window, keep=keep, sink=sink)
             return
-    if not special and kernels.attention_prefill_tc5(q, batch.n_tokens, out, k_cache, v_cache, block_table, batch.seq_slot,
+    if kernels.attention_prefill_tc5(q, batch.n_tokens, out, k_cache, v_cache, block_table, batch.seq_slot,
                                      batch.cu_q, batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv,
-                                     hd, scale, window, max_kv_len=batch.max_kv_len):
+                                     hd, scale, window, max_kv_len=batch.max_kv_len, keep=keep, sink=sink):
         return
-    if not special and kernels.attention_prefill(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
-                                                 batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
-                                                 scale, window):
+    if kernels.attention_prefill(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
+                                 batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
+                                 scale, window, keep=keep, sink=sink):
         return
     kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                               batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,

@@ -611,6 +611,135 @@ def test_attention_decode_split_kv(case, fast):
     assert err < 2e-2, err
 
 
+def kept_reference(ks, vs, qs, window, keep, sink, scale):
+    """Row i sees key j when j <= i and (i - j < window or j < keep); with a sink the denominator has exp(sink) more."""
+    outs = []
+    for k, v, q in zip(ks, vs, qs):
+        n, ql = k.shape[0], q.shape[0]
+        H, G = q.shape[1], k.shape[1]
+        i = torch.arange(n - ql, n)[:, None]
+        j = torch.arange(n)[None, :]
+        seen = (j <= i) & (((i - j) < (window or n + 1)) | (j < keep))
+        o = torch.empty(ql, H, v.shape[-1], dtype=torch.float64)
+        for h in range(H):
+            s = (q[:, h].double() @ k[:, h // (H // G)].double().t()) * scale
+            s = s.masked_fill(~seen, float("-inf"))
+            m = s.max(-1, keepdim=True).values
+            e = torch.exp(s - m)
+            den = e.sum(-1, keepdim=True) + (torch.exp(sink - m) if sink is not None else 0.0)
+            o[:, h] = (e / den) @ v[:, h // (H // G)].double()
+        outs.append(o)
+    return torch.cat(outs, 0)
+
+
+def forget_pages_between(lens, q_lens, window, keep, kc, vc, meta):
+    """What a cache gives back: pages wholly between the kept positions and the window of the step's first query.
+    Their table entries become -1 and the pages NaN, so a kernel that touched them would show."""
+    if window is None:
+        return
+    for b, (n, ql) in enumerate(zip(lens, q_lens)):
+        first_needed = max(0, n - ql - window + 1)
+        slot = int(meta["seq_slot"][b])
+        for p in range((keep + 63) // 64, first_needed // 64):
+            page = int(meta["table"][slot, p])
+            kc[page], vc[page] = float("nan"), float("nan")
+            meta["table"][slot, p] = -1
+
+
+KEEP_CASES = [
+    # lens, q_lens, nq, nkv, hd, window, keep, sink
+    ([700, 130], [700, 100], 4, 2, 64, 100, 20, 0.0),              # whole and a piece; kept positions inside the first page
+    ([900], [333], 6, 1, 64, 200, 70, None),                       # kept positions over a page border; no sink
+    ([520, 257], [300, 130], 2, 2, 128, 130, 64, 0.5),             # kept positions of exactly a page
+    ([1000, 333], [1000, 77], 4, 2, 128, 40, 6, 0.0),              # a window narrower than a page
+    ([513], [513], 2, 1, 256, 150, 129, -1.0),
+    ([400, 64], [400, 64], 2, 2, 128, None, 0, 0.0),               # no window: the sink alone
+    ([300], [300], 2, 1, 64, 300, 10, None),                       # a window that never leaves a key out
+    ([640, 449], [128, 1], 2, 2, 64, 64, 1, 3.0),                  # pieces that start on a page border; one kept position
+    ([700, 1, 129, 64, 333], [1] * 5, 8, 2, 64, 130, 6, 0.0),      # single tokens from here on
+    ([513, 40, 1100], [1] * 3, 6, 3, 128, 70, 64, None),
+    ([1000, 300], [1, 1], 32, 2, 128, 300, 100, 6.0),              # 16 query heads a group
+    ([257, 100, 31], [1] * 3, 12, 2, 64, 33, 33, 2.0),
+    ([900], [1], 2, 2, 256, 100, 200, 8.0),                        # more kept positions than the window is long
+    ([700, 200], [1, 1], 4, 2, 64, None, 0, 4.0),                  # no window: the sink alone
+]
+
+
+@pytest.mark.parametrize("case", range(len(KEEP_CASES)))
+def test_attention_kernels_keep_the_first_positions_and_take_a_sink(case):
+    """Every attention kernel: a window beside which the first positions stay visible, and a softmax whose
+    denominator has one more term.  The last query of every sequence looks for the key just outside its window, the
+    key just inside, the last kept key and the first that is not kept."""
+    from rocml_b200 import kernels
+    lens, q_lens, nq, nkv, hd, window, keep, sink = KEEP_CASES[case]
+    dtype = torch.bfloat16
+    ks, vs, qs, kc, vc, meta = paged_case(300 + case, lens, q_lens, nq, nkv, hd, dtype)
+    g = torch.Generator().manual_seed(case)
+    for b, n in enumerate(lens):
+        if window is None or n <= window + keep + 2:
+            continue
+        for j in [n - 1 - window, n - window] + ([keep - 1, keep] if keep else []):
+            ks[b][j] = (qs[b][-1][:: nq // nkv] * (0.8 + 0.1 * torch.rand(1, generator=g))).to(dtype).float()
+            kc[int(meta["table"][meta["seq_slot"][b], j // 64]), :, j % 64] = ks[b][j]
+    forget_pages_between(lens, q_lens, window, keep, kc, vc, meta)
+    scale = 1.0 / math.sqrt(hd)
+    want = kept_reference(ks, vs, qs, window, keep, sink, scale)
+    if window is not None and any(n > window + keep + 2 for n in lens):      # the marked keys matter
+        assert (kept_reference(ks, vs, qs, window + 1, keep, sink, scale) - want).abs().max() > 0.05
+        assert (kept_reference(ks, vs, qs, window, keep - 1, sink, scale) - want).abs().max() > 0.05
+        assert (kept_reference(ks, vs, qs, window, keep + 1, sink, scale) - want).abs().max() > 0.05
+    if sink is not None:
+        assert (kept_reference(ks, vs, qs, window, keep, None, scale) - want).abs().max() > 1e-3
+    q = torch.cat(qs, 0).reshape(-1, nq * hd).to(dtype).to(DEV)
+    d = {k: v.to(DEV) for k, v in meta.items()}
+    kc, vc = kc.to(dtype).to(DEV), vc.to(dtype).to(DEV)
+    B, T = len(lens), q.shape[0]
+
+    def check(out, what):
+        err = (out.cpu().double().reshape(want.shape) - want).abs().max().item()
+        assert err < 2e-2, (what, err)
+
+    out = torch.full_like(q, float("nan"))
+    kernels.attention_generic(q, out, kc, vc, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"], B, max(q_lens), nq, nkv, hd,
+                              scale, window or 0, keep=keep, sink=sink)
+    check(out, "plain")
+    out = torch.full_like(q, float("nan"))
+    assert kernels.attention_prefill(q, out, kc, vc, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"], B, max(q_lens), nq, nkv,
+                                     hd, scale, window or 0, keep=keep, sink=sink)
+    check(out, "mma.sync")
+    out = torch.full_like(q, float("nan"))
+    assert kernels.attention_prefill_tc5(q, T, out, kc, vc, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"], B, max(q_lens),
+                                         nq, nkv, hd, scale, window or 0, max_kv_len=max(lens), keep=keep, sink=sink)
+    kernels.check_status(DEV)
+    check(out, "tcgen05")
+    if max(q_lens) > 1:
+        return
+    n_pages = (max(lens) + 63) // 64
+    for ppb in (1, 3, n_pages, 0):
+        n_chunks = B + 6 if ppb == 0 else (n_pages + ppb - 1) // ppb + 1
+        acc = torch.full((B, nq, n_chunks, hd), float("nan"), dtype=torch.float32, device=DEV)
+        ml = torch.full((B, nq, n_chunks, 2), float("nan"), dtype=torch.float32, device=DEV)
+        out = torch.full_like(q, float("nan"))
+        took = kernels.attention_decode(q, out, kc, vc, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"], B, nq, nkv, hd,
+                                        scale, window or 0, n_chunks, acc, ml, ppb, keep=keep, sink=sink)
+        if ppb == 0 and keep and window:
+            assert not took          # equal shares of all pages have no place for pages apart from the window's
+            continue
+        assert took
+        assert int(kernels.decode_counters(DEV).abs().sum()) == 0
+        check(out, f"decode, {ppb} pages a block")
+        # the plain kernel in pages, merged
+        out = torch.full_like(q, float("nan"))
+    acc = torch.full((B, nq, n_pages, hd), float("nan"), dtype=torch.float32, device=DEV)
+    ml = torch.full((B, nq, n_pages, 2), float("nan"), dtype=torch.float32, device=DEV)
+    out = torch.full_like(q, float("nan"))
+    kernels.attention_generic(q, out, kc, vc, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"], B, 1, nq, nkv, hd, scale,
+                              window or 0, 64, n_pages, acc, ml, keep=keep, sink=sink)
+    kernels.attention_merge(acc, ml, out, (d["kv_len"] - 1).to(torch.int32), d["seq_slot"], B, nq, hd, 64, n_pages, window or 0,
+                            keep=keep, sink=sink)
+    check(out, "plain, split and merged")
+
+
 @pytest.mark.parametrize("lens,nq,nkv,window,S,norm,rope,grid", [
     ([700, 1, 129, 64, 128], 32, 8, None, 7, True, True, (1, 1)),      # one page per block: clusters of up to 12
     ([300, 131, 65], 8, 2, None, 1, True, True, (2, 3)),               # clusters of 2

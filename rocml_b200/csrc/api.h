@@ -165,13 +165,14 @@ int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void* out, int 
                              const void* v_cache, int n_pages, const int* block_table, int max_pages,
                              const int* seq_slot, const int* cu_q, const int* kv_len, int B, int max_q_len, int nq,
                              int nkv, int hd, float scale, int window, int keep, float sink, int heads_first, int* status,
-                             void* stream);
+                             const void* gate, long long gate_row_stride, void* stream);
 
 int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                         const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                         const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window, int keep, float sink,
                         int n_chunks, int pages_per_block, float* part_acc, float* part_ml, int* counters, void* out,
-                        int o_stride, void* stream);
+                        int o_stride, const void* gate, int gate_f32, int gate_n_in, long long gate_in_stride,
+                        long long gate_row_stride, void* stream);
 
 int rb_attention_decode_fused(const float* proj, int n_in, long long in_stride, int row_stride, const void* q_norm_w,
                               const void* k_norm_w, int w_f32, float eps, const float* cos_sin, int write_kv,

@@ -82,6 +82,7 @@ struct Projections {
     int row_groups;
     long long row_sumsq_ld;
     float row_eps, row_inv_width;
+    GateCols gate;            // what the result is multiplied by before it is written (raw null: nothing)
 };
 
 // One head of 128 values, 4 per lane: the sum of the partial sums, then (what != 2) RMSNorm with `w`
@@ -590,7 +591,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             part_acc[pidx * HD + d] = A;
             if (d == 0) { part_ml[pidx * 2] = M; part_ml[pidx * 2 + 1] = L; }
         } else {
-            out[(size_t)t * o_stride + (size_t)head * HD + d] = __float2bfloat16_rn(finished(A, L, M, sink));
+            float y = finished(A, L, M, sink);
+            if (pj.gate.raw) y *= gate_factor(pj.gate, (size_t)t, (size_t)head * HD + d);
+            out[(size_t)t * o_stride + (size_t)head * HD + d] = __float2bfloat16_rn(y);
         }
     }
     if (CL) {
@@ -628,7 +631,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                     A = fmaf(wt, pa[i], A);
                 }
             }
-            out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(finished(A, L, MM, sink));
+            float y = finished(A, L, MM, sink);
+            if (pj.gate.raw) y *= gate_factor(pj.gate, (size_t)t, (size_t)(h0 + r) * HD + d);
+            out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(y);
         }
         cluster_sync_all();                                  // nobody leaves while its part may still be read
         return;
@@ -677,7 +682,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             L = fmaf(wt, pl[i], L);
             A = fmaf(wt, __ldcg(pa + (size_t)i * HD), A);
         }
-        out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(finished(A, L, MM, sink));
+        float y = finished(A, L, MM, sink);
+        if (pj.gate.raw) y *= gate_factor(pj.gate, (size_t)t, (size_t)(h0 + r) * HD + d);
+        out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(y);
     }
    }
 round_done:
@@ -799,8 +806,13 @@ extern "C" int rb_attention_decode(const void* q, int q_stride, const void* k_ca
                                    const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                                    const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
                                    int keep, float sink, int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
-                                   int* counters, void* out, int o_stride, void* stream) {
+                                   int* counters, void* out, int o_stride, const void* gate, int gate_f32, int gate_n_in,
+                                   long long gate_in_stride, long long gate_row_stride, void* stream) {
     Projections none = {};
+    if (gate != nullptr) {      // nq * hd columns of the projection rows: the result times their sigmoid
+        if (gate_n_in < 1) return RB_ERR_BAD_SIZE;
+        none.gate = GateCols{gate, gate_f32, gate_n_in, gate_in_stride, gate_row_stride};
+    }
     return decode_entry(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, nkv, hd,
                         scale, window, keep, sink, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, none, stream);
 }
@@ -826,7 +838,7 @@ extern "C" int rb_attention_decode_fused(const float* proj, int n_in, long long 
     if (hd != 128 || proj == nullptr || n_in < 1) return RB_ERR_BAD_SIZE;
     if (((uintptr_t)proj & 15) || (in_stride % 4) || (row_stride % 4) || ((uintptr_t)cos_sin & 7)) return RB_ERR_BAD_ALIGN;
     if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return RB_ERR_BAD_SIZE;
-    Projections pj;
+    Projections pj = {};
     pj.proj = proj; pj.n_in = n_in; pj.in_stride = in_stride; pj.row_stride = row_stride;
     pj.q_norm_w = q_norm_w; pj.k_norm_w = k_norm_w; pj.w_f32 = w_f32; pj.eps = eps;
     pj.cos_sin = reinterpret_cast<const float2*>(cos_sin);
@@ -905,5 +917,5 @@ extern "C" int rb_attention_decode_static(const void* q, int q_stride, const voi
     if (e != cudaSuccess) return (int)e;
     return rb_attention_decode(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, n_seqs,
                                nq, nkv, hd, scale, window, 0, RB_NO_SINK, n_chunks, 1, sc->acc, sc->ml, sc->counters, out, o_stride,
-                               stream);
+                               nullptr, 0, 0, 0, 0, stream);
 }

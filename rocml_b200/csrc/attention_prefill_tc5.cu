@@ -116,7 +116,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slot,
                              const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
                              float scale, int window, int keep, float sink, int heads_first, int strict_order,
-                             int* __restrict__ status) {
+                             int* __restrict__ status, const __nv_bfloat16* __restrict__ gate, long long gate_row_stride) {
     using Z = Sizes<HD>;
     constexpr int HALVES = Z::HALVES, Q_BYTES = Z::Q_BYTES, KV_TILE = Z::KV_TILE, Q_HALF = Z::Q_HALF, KV_HALF = Z::KV_HALF;
     constexpr int TILE_BYTES = Z::TILE_BYTES, SMEM_BYTES = Z::SMEM_BYTES, TMEM_COLS = Z::TMEM_COLS;
@@ -382,12 +382,25 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (rb::has_sink(sink)) l_sum += exp2f(fminf(sink * LOG2E - m_used, 126.f));
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             __nv_bfloat16* orow = out + (size_t)(q0 + m0 + r) * o_stride + (size_t)head * HD;
+            // a gate for every value: columns of the token's projection row, whose sigmoid (32-bit) multiplies the result
+            const __nv_bfloat16* grow = gate ? gate + (size_t)(q0 + m0 + r) * gate_row_stride + (size_t)head * HD : nullptr;
 #pragma unroll 1
             for (int c = 0; c < HD / 16; ++c) {
                 float ov[16];
                 tmem_ld16(lane_base + 2 * BNK + c * 16, ov);
                 if (r < rows_here) {
                     uint32_t w[8];
+                    if (grow) {
+                        const uint4 g0 = reinterpret_cast<const uint4*>(grow + c * 16)[0];
+                        const uint4 g1 = reinterpret_cast<const uint4*>(grow + c * 16)[1];
+                        const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+                            ov[2 * i] *= rb::sigmoid_f32(z.x);
+                            ov[2 * i + 1] *= rb::sigmoid_f32(z.y);
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         __nv_bfloat162 h = __floats2bfloat162_rn(ov[2 * i] * inv, ov[2 * i + 1] * inv);
@@ -464,7 +477,7 @@ template <int HD>
 int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, const void* k_cache, const void* v_cache,
                int n_pages, const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                const int* kv_len, int B, int max_q_len, int nq, int nkv, float scale, int window, int keep, float sink,
-               int heads_first, int* status, cudaStream_t stream) {
+               int heads_first, int* status, const void* gate, long long gate_row_stride, cudaStream_t stream) {
     // RB_PREFILL_STRICT_ORDER=0: see `strict_order` in the kernel's MMA thread
     static const int strict_order = [] { const char* e = getenv("RB_PREFILL_STRICT_ORDER"); return (e && e[0] == '0') ? 0 : 1; }();
     CUtensorMap mq, mk, mv;
@@ -485,7 +498,7 @@ int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, cons
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((k), grid, dim3(192), Sizes<HD>::SMEM_BYTES, stream, mq, mk, mv, (__nv_bfloat16*)out, o_stride,
               block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, keep, sink, heads_first, strict_order,
-              status);
+              status, (const __nv_bfloat16*)gate, gate_row_stride);
     return RB_OK;
 }
 }  // namespace
@@ -493,21 +506,23 @@ int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, cons
 // q rows [T, q_stride] bfloat16 (T = tokens of the step), caches [n_pages, nkv, 64, hd].  heads_first: the order
 // in which blocks start (see the kernel); it changes no result.  keep: beside a window the keys at positions below
 // it stay visible; sink: a score whose exponential joins every row's denominator (RB_NO_SINK: none).  Head sizes 64, 128 and 256;
-// RB_ERR_BAD_SIZE / RB_ERR_BAD_ALIGN otherwise (the caller then uses the mma.sync kernel).
+// RB_ERR_BAD_SIZE / RB_ERR_BAD_ALIGN otherwise (the caller then uses the mma.sync kernel).  gate: nq * hd bfloat16 columns of
+// the tokens' projection rows (gate_row_stride elements apart), or null: the result is multiplied by their sigmoid.
 extern "C" int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void* out, int o_stride,
                                         const void* k_cache, const void* v_cache, int n_pages,
                                         const int* block_table, int max_pages, const int* seq_slot,
                                         const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv,
                                         int hd, float scale, int window, int keep, float sink, int heads_first,
-                                        int* status, void* stream) {
+                                        int* status, const void* gate, long long gate_row_stride, void* stream) {
     if (B <= 0 || max_q_len <= 0 || T <= 0) return RB_OK;
+    if (gate && (((uintptr_t)gate & 15) || (gate_row_stride % 8))) return RB_ERR_BAD_ALIGN;
     if ((hd != 64 && hd != 128 && hd != 256) || nkv <= 0 || nq % nkv || keep < 0) return RB_ERR_BAD_SIZE;
     if (window <= 0) keep = 0;                            // kept first keys stand beside a window only
     if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15) ||
         (q_stride % 8) || (o_stride % 8))
         return RB_ERR_BAD_ALIGN;
 #define RB_TC5_ARGS q, q_stride, T, out, o_stride, k_cache, v_cache, n_pages, block_table, max_pages, seq_slot, cu_q, kv_len, \
-                    B, max_q_len, nq, nkv, scale, window, keep, sink, heads_first, status, (cudaStream_t)stream
+                    B, max_q_len, nq, nkv, scale, window, keep, sink, heads_first, status, gate, gate_row_stride, (cudaStream_t)stream
     if (hd == 64) return launch_tc5<64>(RB_TC5_ARGS);
     if (hd == 128) return launch_tc5<128>(RB_TC5_ARGS);
     return launch_tc5<256>(RB_TC5_ARGS);

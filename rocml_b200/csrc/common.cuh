@@ -104,6 +104,28 @@ __device__ __forceinline__ float add_sink(float m, float& l, float sink) {
     return a;
 }
 
+// Columns of the step's projection rows that gate an attention kernel's result value by value, so that no kernel
+// of its own has to: out[t][c] *= sigmoid(sum over the partial sums of raw[s][t][c]), formed in 32-bit.
+struct GateCols {
+    const void* raw;        // the first gate column of the first token's row; null: no gate
+    int f32;                // the columns' type: float32, or bfloat16
+    int n_in;               // partial sums, added in order
+    long long in_stride;    // elements between two partial sums
+    long long row_stride;   // elements between two tokens
+};
+__device__ __forceinline__ float sigmoid_f32(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float gate_factor(const GateCols& g, size_t t, size_t col) {
+    float z = 0.f;
+    if (g.f32) {
+        const float* p = static_cast<const float*>(g.raw) + t * g.row_stride + col;
+        for (int s = 0; s < g.n_in; ++s) z += p[(size_t)s * g.in_stride];
+    } else {
+        const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(g.raw) + t * g.row_stride + col;
+        for (int s = 0; s < g.n_in; ++s) z += __bfloat162float(p[(size_t)s * g.in_stride]);
+    }
+    return sigmoid_f32(z);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -179,7 +179,18 @@ __device__ __forceinline__ void load_w4(const WT* w, int lane, float* out) {
     }
 }
 
-template <typename IT, typename AT, typename WT>
+// EXT: further options, as in the general kernel.  Only the first `rot_dim` (a multiple of 8) dimensions of a head turn:
+// dimension i < rot_dim / 2 pairs with i + rot_dim / 2, which sits rot_dim / 8 lanes away; `post_norm` divides queries
+// and keys by their root mean square after the rotation; `v_out` keeps the value heads as they came (32-bit) and
+// `v_first` / `v_lambda` blend what is cached with such rows of an earlier layer.
+struct RotateExt {
+    int rot_dim, post_norm;
+    const float* v_first;
+    const float* v_lambda;
+    float* v_out;
+};
+
+template <typename IT, typename AT, typename WT, bool EXT>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride,
                                 AT* __restrict__ q_out, int q_stride, int T, int nq, int nkv,
@@ -187,9 +198,13 @@ qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_s
                                 const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                 const int* __restrict__ slot_of_token, const int* __restrict__ block_table,
                                 int max_pages, AT* __restrict__ k_cache, AT* __restrict__ v_cache, int write_kv,
-                                const float2* __restrict__ cs_table) {
+                                const float2* __restrict__ cs_table, const RotateExt ext) {
     pdl_trigger();
     constexpr int hd = 128;
+    // the lanes that hold a rotation pair's first and second member, and how far apart the two sit
+    const int pair_lanes = EXT ? max(ext.rot_dim >> 3, 1) : 16;
+    const int cs_lane = EXT ? (int)(threadIdx.x & 31) % pair_lanes : (int)(threadIdx.x & 15);
+    const int half = EXT ? ext.rot_dim >> 1 : 64;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     const int groups = (heads_total + HPW - 1) / HPW;             // groups of heads a token
@@ -211,10 +226,14 @@ qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_s
     // together: its angles, and the page of its key and value if this warp holds any.
     float4 cs_a = make_float4(1.f, 0.f, 1.f, 0.f), cs_b = cs_a;
     if (inv_freq && cs_table) {
-        const float4* c4 = reinterpret_cast<const float4*>(cs_table + (size_t)t * 64 + (lane & 15) * 4);
+        const float4* c4 = reinterpret_cast<const float4*>(cs_table + (size_t)t * half + cs_lane * 4);
         cs_a = c4[0];
         cs_b = c4[1];
     }
+    const bool turns = !EXT || lane < 2 * pair_lanes;             // this lane's dimensions take part in the rotation
+    const bool pair_first = EXT ? lane < pair_lanes : lane < 16;
+    const int partner = EXT ? (pair_first ? lane + pair_lanes : (turns ? lane - pair_lanes : lane)) : lane ^ 16;
+    const float lam = (EXT && ext.v_first) ? ext.v_lambda[0] : 0.f;
     int page = -2;
     if (write_kv && h0 + n_heads > nq) page = block_table[(size_t)slot * max_pages + (pos / RB_PAGE)];
     // every head's values: the loads of all heads (and of up to 8 partial sums each) are in flight together
@@ -258,7 +277,7 @@ qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_s
             cs[0] = a.x; sn[0] = a.y; cs[1] = a.z; sn[1] = a.w; cs[2] = b.x; sn[2] = b.y; cs[3] = b.z; sn[3] = b.w;
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) sincosf((float)pos * inv_freq[(lane & 15) * 4 + j], &sn[j], &cs[j]);
+            for (int j = 0; j < 4; ++j) sincosf((float)pos * inv_freq[cs_lane * 4 + j], &sn[j], &cs[j]);
         }
     }
 #pragma unroll
@@ -270,9 +289,17 @@ qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_s
         if (kind == 0) {
             dst = q_out + (size_t)t * q_stride + (size_t)h * hd;
         } else {
-            if (page < 0) continue;                             // no page: the host never schedules this
             const int head = kind == 1 ? h - nq : h - nq - nkv;
+            if (EXT && kind == 2 && ext.v_out)
+                *reinterpret_cast<float4*>(ext.v_out + ((size_t)t * nkv + head) * hd + lane * 4) =
+                    make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+            if (page < 0) continue;                             // no page: the host never schedules this
             dst = (kind == 1 ? k_cache : v_cache) + (((size_t)page * nkv + head) * RB_PAGE + (pos % RB_PAGE)) * hd;
+            if (EXT && kind == 2 && ext.v_first) {
+                const float4 f = *reinterpret_cast<const float4*>(ext.v_first + ((size_t)t * nkv + head) * hd + lane * 4);
+                v[j][0] = (1.f - lam) * v[j][0] + lam * f.x; v[j][1] = (1.f - lam) * v[j][1] + lam * f.y;
+                v[j][2] = (1.f - lam) * v[j][2] + lam * f.z; v[j][3] = (1.f - lam) * v[j][3] + lam * f.w;
+            }
         }
         float (&x)[4] = v[j];
         if (kind != 2) {
@@ -286,9 +313,15 @@ qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_s
                 // dimension i < 64 pairs with i + 64: lanes 0-15 hold x_i, lanes 16-31 the partners
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
-                    x[i] = lane < 16 ? x[i] * cs[i] - other * sn[i] : other * sn[i] + x[i] * cs[i];
+                    const float other = __shfl_sync(0xffffffffu, x[i], partner);
+                    if (turns) x[i] = pair_first ? x[i] * cs[i] - other * sn[i] : other * sn[i] + x[i] * cs[i];
                 }
+            }
+            if (EXT && ext.post_norm) {
+                const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+                const float inv = rsqrtf(ss / (float)hd + eps);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) x[i] *= inv;
             }
         }
         if (sizeof(AT) == 4) {
@@ -315,16 +348,21 @@ static int launch_qk(const void* in, int n_in, long long in_stride, int row_stri
     const long long blocks = (items + warps - 1) / warps;
     if (blocks > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
     const size_t esz = sizeof(IT);
-    if (hd == 128 && vd == 128 && hdp == 128 && n_gate == 0 && !post_norm && !v_first && !v_out && !(inv_freq && interleaved) &&
-        (!inv_freq || rot_dim == 128) && (((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)k_cache |
-                                                        (uintptr_t)v_cache | (uintptr_t)qw | (uintptr_t)kw |
-                                                        (uintptr_t)cs_table) & 15) == 0 &&
+    if (hd == 128 && vd == 128 && hdp == 128 && n_gate == 0 && !(inv_freq && interleaved) &&
+        (!inv_freq || rot_dim % 8 == 0) && (((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)k_cache |
+                                                          (uintptr_t)v_cache | (uintptr_t)qw | (uintptr_t)kw |
+                                                          (uintptr_t)cs_table | (uintptr_t)v_first | (uintptr_t)v_out) & 15) == 0 &&
         (row_stride * esz) % 16 == 0 && ((size_t)in_stride * esz) % 16 == 0 && (q_stride * sizeof(AT)) % 16 == 0) {
         const long long groups = (long long)T * ((nq + (write_kv ? 2 * nkv : 0) + HPW - 1) / HPW);
-        RB_LAUNCH((qk_norm_rope_cache_hd128_kernel<IT, AT, WT>), dim3((int)((groups + 3) / 4)), dim3(128), 0, s, (const IT*)in, n_in,
-                  (size_t)in_stride, row_stride, (AT*)q_out, q_stride, T, nq, nkv, (const WT*)qw, (const WT*)kw, eps,
-                  inv_freq, positions, slot_of_token, block_table, max_pages, (AT*)k_cache, (AT*)v_cache, write_kv,
-                  cs_table);
+        const bool ext = post_norm || v_first || v_out || (inv_freq && rot_dim != 128);
+        const RotateExt e{inv_freq ? rot_dim : 128, post_norm, v_first, v_lambda, v_out};
+#define RB_QK128(EXT)                                                                                                          \
+        RB_LAUNCH((qk_norm_rope_cache_hd128_kernel<IT, AT, WT, EXT>), dim3((int)((groups + 3) / 4)), dim3(128), 0, s, (const IT*)in, \
+                  n_in, (size_t)in_stride, row_stride, (AT*)q_out, q_stride, T, nq, nkv, (const WT*)qw, (const WT*)kw, eps,    \
+                  inv_freq, positions, slot_of_token, block_table, max_pages, (AT*)k_cache, (AT*)v_cache, write_kv, cs_table, e)
+        if (ext) RB_QK128(true);
+        else RB_QK128(false);
+#undef RB_QK128
         return RB_OK;
     }
     const size_t smem = (size_t)warps * hdp * sizeof(float);

@@ -141,9 +141,9 @@ def _lib():
         lib.rb_attention_prefill.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                              _f, _i, _i, _f, _vp]
         lib.rb_attention_prefill_tc5.argtypes = [_vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i,
-                                                 _i, _i, _i, _f, _i, _i, _f, _i, _vp, _vp]
+                                                 _i, _i, _i, _f, _i, _i, _f, _i, _vp, _vp, _ll, _vp]
         lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _f, _i,
-                                            _i, _vp, _vp, _vp, _vp, _i, _vp]
+                                            _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _ll, _ll, _vp]
         lib.rb_attention_decode_fused.argtypes = [_vp, _i, _ll, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _i, _ll, _f, _i,
                                                   _vp, _vp, _vp, _i, _vp, _vp,
                                                   _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]
@@ -421,16 +421,20 @@ def prefill_heads_first(n_seqs: int, nkv: int, hd: int, max_kv_len: int, window:
 def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                           block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                           n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
-                          max_kv_len: Optional[int] = None, keep: int = 0, sink: Optional[float] = None) -> bool:
+                          max_kv_len: Optional[int] = None, keep: int = 0, sink: Optional[float] = None,
+                          gate: Optional[torch.Tensor] = None) -> bool:
     """bfloat16 flash attention with tcgen05 (accumulators in tensor memory, TMA loads), head sizes 64, 128 and 256.
     ``keep``: beside a window the keys at positions below it stay visible; ``sink``: a score whose exponential
-    joins every row's denominator.
+    joins every row's denominator.  ``gate``: bfloat16 [T, nq * hd] columns of the projection rows (a view with
+    unit stride along a row); the result is multiplied by their sigmoid before it is written.
     ``max_kv_len`` (the longest context of the step; the longest query if not given) only decides the
     order in which blocks start: the longest blocks of all heads first while the keys and values that
     the step reads fit the L2 cache, one head after another beyond.  Returns False when the kernel
     does not take the head size or the alignment."""
     if hd not in (64, 128, 256) or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or \
             q.stride(-1) != 1 or out.stride(-1) != 1 or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        return False
+    if gate is not None and (gate.dtype != torch.bfloat16 or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != (n_tokens, nq * hd)):
         return False
     if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
         raise KernelError("attention_prefill_tc5: cache must be [pages, nkv, 64, hd]")
@@ -439,7 +443,7 @@ def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_c
         _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"),
         _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window), int(keep), _sink(sink),
         1 if prefill_heads_first(n_seqs, nkv, hd, max_q_len if max_kv_len is None else max_kv_len, window) else 0,
-        _ptr(status_word(q.device)), _stream())
+        _ptr(status_word(q.device)), _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
     if rc in (10001, 10003):
         return False
     _check(rc, "attention_prefill_tc5")
@@ -532,9 +536,12 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                      block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                      n_seqs: int, nq: int, nkv: int, hd: int, scale: float, window: int, n_chunks: int,
                      part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
-                     pages_per_block: int = 1, keep: int = 0, sink: Optional[float] = None) -> bool:
+                     pages_per_block: int = 1, keep: int = 0, sink: Optional[float] = None,
+                     gate: Optional[torch.Tensor] = None) -> bool:
     """``keep``: the keys at positions below it stay visible beside the window (not with ``pages_per_block`` 0);
-    ``sink``: a score whose exponential joins every row's denominator.
+    ``sink``: a score whose exponential joins every row's denominator.  ``gate``: [T, nq * hd] or [S, T, nq * hd]
+    (partial sums, added in order) columns of the projection rows, bfloat16 or float32, unit stride along a row: the
+    result is multiplied by their sigmoid before it is written.
     bfloat16 decode attention, one query token per sequence; a block takes ``pages_per_block``
     pages of 64 keys, ``n_chunks`` blocks cover the longest sequence and are merged by the kernel
     itself; part_acc / part_ml [T, nq, >= n_chunks, ...] are its work space when n_chunks > 1.
@@ -548,12 +555,18 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
         raise KernelError("attention_decode: cache must be [pages, nkv, 64, hd]")
     _check_parts(part_acc, part_ml, n_chunks, "attention_decode")
+    g_n, g_in, g_row = 0, 0, 0
+    if gate is not None:
+        if gate.dtype not in (torch.bfloat16, torch.float32) or gate.dim() not in (2, 3) or gate.stride(-1) != 1 or \
+                gate.shape[-1] != nq * hd:
+            return False
+        g_n, g_in, g_row = (gate.shape[0], gate.stride(0), gate.stride(1)) if gate.dim() == 3 else (1, 0, gate.stride(0))
     rc = _lib().rb_attention_decode(
         _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"), block_table.shape[1],
         _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs, nq, nkv, hd, float(scale),
         int(window), int(keep), _sink(sink), int(n_chunks), int(pages_per_block), _ptr(part_acc), _ptr(part_ml),
         _ptr(decode_counters(q.device)), _ptr(out),
-        out.stride(0), _stream())
+        out.stride(0), _ptr(gate), 1 if gate is not None and gate.dtype == torch.float32 else 0, g_n, g_in, g_row, _stream())
     if rc in (10001, 10003):
         return False
     _check(rc, "attention_decode")

@@ -255,9 +255,15 @@ class Attention(Mixer):
                 gates=gates, post_norm=self.qk_unit_norm, v_first=v_first, v_lambda=self.v_lambda if v_first is not None else None,
                 v_out=v_out)
         attn = torch.empty((T, self.nq * self.hdp), dtype=act, device=dev)
-        paged_attention(q, attn, batch, view.k, view.v, view.block_table, self.nq, self.nkv, self.hdp, self.scale, window,
-                        keep=self.keep_first, sink=self.sink)
-        if self.gated or self.hdp != self.vd:
+        # a gate for every value of heads that carry no padding: the attention kernel that takes the projection's gate
+        # columns multiplies its result by their sigmoid as it writes it
+        raw_gate = None
+        if self.gate_per_value and self.hdp == self.vd:
+            off = self.nq * self.hd + self.nkv * (self.hd + self.vd)
+            raw_gate = proj[..., off:off + self.nq * self.vd]
+        gated_inside = paged_attention(q, attn, batch, view.k, view.v, view.block_table, self.nq, self.nkv, self.hdp, self.scale,
+                                       window, keep=self.keep_first, sink=self.sink, gate=raw_gate)
+        if (self.gated and not gated_inside) or self.hdp != self.vd:
             narrow = torch.empty((T, self.nq * self.vd), dtype=act, device=dev)
             raw = None
             if self.gate_per_value:          # the gate's columns of the projection rows, as they are: the kernel takes the sigmoid
@@ -327,12 +333,14 @@ class Attention(Mixer):
         paged_attention(q, out, batch, view.k, view.v, view.block_table, self.nq, self.nkv, self.hd, self.scale, window)
 
 
-def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window, keep=0, sink=None):
+def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window, keep=0, sink=None, gate=None) -> bool:
     """Softmax attention of the step's queries (rows of nq heads of ``hd``) over paged keys and values
     [pages, nkv, 64, hd], causal, inside ``window`` when it is not 0 (and the first ``keep`` positions beside it);
     ``sink``: a score whose exponential joins every row's denominator.  One token per sequence:
     keys split in fixed chunks, partial results merged; otherwise whole rows.  Any mixer whose cache is
-    such pages calls this (keys and values may be the same tensor)."""
+    such pages calls this (keys and values may be the same tensor).  ``gate``: nq * hd columns of the step's projection
+    rows ([T, ..] or partial sums [S, T, ..]); a kernel that takes them multiplies its result by their sigmoid.
+    Returns whether that was done: if not, the result is as without ``gate`` and the caller gates it."""
     if batch.is_decode:
         chunk = DECODE_CHUNK
         T = batch.n_tokens
@@ -351,25 +359,27 @@ def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, s
             ml = torch.empty((T, nq, parts, 2), dtype=torch.float32, device=q.device)
         fast = kernels.attention_decode(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                                         batch.kv_len, batch.n_seqs, nq, nkv, hd, scale,
-                                        window, n_blocks, acc, ml, ppb, keep=keep, sink=sink)
+                                        window, n_blocks, acc, ml, ppb, keep=keep, sink=sink, gate=gate)
         n_chunks = n_pages
         if fast:
-            return
+            return gate is not None
         if n_chunks > 1:
             kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                                       batch.kv_len, batch.n_seqs, 1, nq, nkv, hd, scale,
                                       window, chunk, n_chunks, acc, ml, keep=keep, sink=sink)
             kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, nq, hd,
                                     chunk, n_chunks, window, keep=keep, sink=sink)
-            return
+            return False
+    tc5_gate = gate if gate is not None and gate.dim() == 2 and gate.dtype == torch.bfloat16 else None
     if kernels.attention_prefill_tc5(q, batch.n_tokens, out, k_cache, v_cache, block_table, batch.seq_slot,
                                      batch.cu_q, batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv,
-                                     hd, scale, window, max_kv_len=batch.max_kv_len, keep=keep, sink=sink):
-        return
+                                     hd, scale, window, max_kv_len=batch.max_kv_len, keep=keep, sink=sink, gate=tc5_gate):
+        return tc5_gate is not None
     if kernels.attention_prefill(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                                  batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
                                  scale, window, keep=keep, sink=sink):
-        return
+        return False
     kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                               batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
                               scale, window, keep=keep, sink=sink)
+    return False

@@ -69,7 +69,10 @@ def test_frequencies_blended_along_a_ramp(rot):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nq, nkv, hd, vd, rot_dims, parts, order", [
     (4, 2, 32, 16, 16, 1, "rotate_then_unit"), (3, 3, 20, 28, 12, 3, "norm_then_rotate"), (8, 1, 64, 48, 64, 2, "rotate_then_unit"),
-    (2, 2, 128, 64, 32, 1, "norm_then_rotate"), (5, 1, 16, 16, 0, 1, "rotate_then_unit"), (2, 1, 128, 128, 128, 4, "rotate_then_unit")])
+    (2, 2, 128, 64, 32, 1, "norm_then_rotate"), (5, 1, 16, 16, 0, 1, "rotate_then_unit"), (2, 1, 128, 128, 128, 4, "rotate_then_unit"),
+    # heads of 128 on both sides take the kernel with four dimensions a lane: part of a head turns, by 1 to 16 lanes
+    (4, 2, 128, 128, 64, 1, "norm_then_rotate"), (3, 1, 128, 128, 40, 2, "rotate_then_unit"), (6, 3, 128, 128, 8, 1, "rotate_then_unit"),
+    (5, 5, 128, 128, 120, 8, "norm_then_rotate"), (2, 2, 128, 128, 0, 1, "rotate_then_unit")])
 def test_rotation_norms_and_blended_values(dtype, nq, nkv, hd, vd, rot_dims, parts, order):
     """Queries and keys: a weighted per-head norm before the rotation, or a division by the root mean square after
     it; rotate-half over the first rot_dims entries with a magnitude on cosines and sines; value heads of another
@@ -203,6 +206,19 @@ def test_attention_with_kept_first_positions_and_one_more_term(case, dtype):
                     keep=keep, sink=0.0 if sink else None)
     err = (out.cpu().double().reshape(want.shape) - want).abs().max().item()
     assert err < tol, ("library's choice", err)
+    if dtype == "bfloat16":
+        # a gate for every value, taken by the attention kernel from columns of the projection rows: in one piece, and
+        # (single tokens) as partial sums that are added first; the kernels for heads of 64, 128 and 256 take it
+        forms = [torch.randn(T, 8 + nq * hd, generator=g).to(dt)] + ([torch.randn(3, T, 8 + nq * hd, generator=g)] if is_decode else [])
+        for rows in forms:
+            out = torch.full_like(q, float("nan"))
+            done = paged_attention(q, out, batch, kc.to(dt).to(DEV), vc.to(dt).to(DEV), d["table"], nq, nkv, hd, scale, window or 0,
+                                   keep=keep, sink=0.0 if sink else None, gate=rows.to(DEV)[..., 8:])
+            assert done == (hd in (64, 128, 256))
+            z = (rows.double().sum(0) if rows.dim() == 3 else rows.double())[:, 8:]
+            gated = want * torch.sigmoid(z).reshape(want.shape) if done else want
+            err = (out.cpu().double().reshape(want.shape) - gated).abs().max().item()
+            assert err < tol, ("gated inside", done, err)
     out = torch.full_like(q, float("nan"))
     kernels.attention_generic(q, out, kc.to(dt).to(DEV), vc.to(dt).to(DEV), d["table"], d["seq_slot"], d["cu_q"], d["kv_len"],
                               len(lens), max(q_lens), nq, nkv, hd, scale, window or 0, keep=keep, sink=0.0 if sink else None)

@@ -375,6 +375,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             // this tile's count while the slow warp's rows of P are still missing.
             mbar_arrive(&bar->p_full[j & 1]);
         }
+        // a gate for every value: columns of the token's projection row, whose sigmoid (32-bit) multiplies the result.
+        // They do not depend on this kernel's work: the first 16 are asked for before the wait for the last product,
+        // and the next 16 are in flight while 16 values are finished.
+        const bool row_here = r < rows_here;
+        const uint4* grow = (gate && row_here)
+            ? reinterpret_cast<const uint4*>(gate + (size_t)(q0 + m0 + r) * gate_row_stride + (size_t)head * HD) : nullptr;
+        uint4 g0 = make_uint4(0u, 0u, 0u, 0u), g1 = g0;
+        if (grow) { g0 = grow[0]; g1 = grow[1]; }
         if (alive) alive = __all_sync(0xffffffffu, wait_or_abort(&bar->o_final, 0, &bar->abort_flag));
         if (alive) {
             tc_fence_after();
@@ -382,23 +390,20 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (rb::has_sink(sink)) l_sum += exp2f(fminf(sink * LOG2E - m_used, 126.f));
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             __nv_bfloat16* orow = out + (size_t)(q0 + m0 + r) * o_stride + (size_t)head * HD;
-            // a gate for every value: columns of the token's projection row, whose sigmoid (32-bit) multiplies the result
-            const __nv_bfloat16* grow = gate ? gate + (size_t)(q0 + m0 + r) * gate_row_stride + (size_t)head * HD : nullptr;
 #pragma unroll 1
             for (int c = 0; c < HD / 16; ++c) {
                 float ov[16];
                 tmem_ld16(lane_base + 2 * BNK + c * 16, ov);
-                if (r < rows_here) {
+                const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                if (grow && c + 1 < HD / 16) { g0 = grow[2 * c + 2]; g1 = grow[2 * c + 3]; }
+                if (row_here) {
                     uint32_t w[8];
                     if (grow) {
-                        const uint4 g0 = reinterpret_cast<const uint4*>(grow + c * 16)[0];
-                        const uint4 g1 = reinterpret_cast<const uint4*>(grow + c * 16)[1];
-                        const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
-                            ov[2 * i] *= rb::sigmoid_f32(z.x);
-                            ov[2 * i + 1] *= rb::sigmoid_f32(z.y);
+                            ov[2 * i] *= __fdividef(1.f, 1.f + __expf(-z.x));
+                            ov[2 * i + 1] *= __fdividef(1.f, 1.f + __expf(-z.y));
                         }
                     }
 #pragma unroll

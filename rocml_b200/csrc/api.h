@@ -180,7 +180,9 @@ int rb_attention_decode_fused(const float* proj, int n_in, long long in_stride, 
                               int row_width, void* k_cache, void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
                               const int* cu_q, const int* kv_len, int B, int nq, int nkv, int hd, float scale,
                               int window, int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
-                              int* counters, void* out, int o_stride, void* stream);
+                              int* counters, void* out, int o_stride, int keep, float sink, int rot_dim, int post_norm,
+                              const float* v_first, const float* v_lambda, float* v_keep, const void* gate, int gate_f32,
+                              int gate_n_in, long long gate_in_stride, long long gate_row_stride, void* stream);
 
 int rb_attention_merge(const float* part_acc, const float* part_ml, void* out, int o_stride, int dtype,
                        const int* positions, const int* slot_of_token, int T, int nq, int hd, int chunk,

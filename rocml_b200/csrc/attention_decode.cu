@@ -83,6 +83,15 @@ struct Projections {
     long long row_sumsq_ld;
     float row_eps, row_inv_width;
     GateCols gate;            // what the result is multiplied by before it is written (raw null: nothing)
+    // Further options of the projection's heads.  rot_dim (0: the whole head): only the first rot_dim dimensions turn,
+    // dimension i < rot_dim / 2 with i + rot_dim / 2, and cos_sin is [T][rot_dim / 2].  post_norm: queries and keys are
+    // divided by their root mean square (with eps) after the rotation.  v_keep: the new value heads as projected, 32-bit
+    // [T][nkv * 128], for later layers; v_first / v_lambda: such rows of an earlier layer and a factor on the device: what
+    // is cached is (1 - lambda) v + lambda v_first.
+    int rot_dim, post_norm;
+    const float* v_first;
+    const float* v_lambda;
+    float* v_keep;
 };
 
 // One head of 128 values, 4 per lane: the sum of the partial sums, then (what != 2) RMSNorm with `w`
@@ -106,8 +115,9 @@ __device__ __forceinline__ void project_head(const Projections& pj, const float*
             wj[0] = a.x; wj[1] = a.y; wj[2] = b.x; wj[3] = b.y;
         }
     }
+    const int pair_lanes = pj.rot_dim > 0 ? pj.rot_dim >> 3 : 16;   // lanes between the two members of a rotation pair
     if (rotate) {
-        const float4* c4 = reinterpret_cast<const float4*>(pj.cos_sin + (size_t)t * 64 + (lane & 15) * 4);
+        const float4* c4 = reinterpret_cast<const float4*>(pj.cos_sin + (size_t)t * (pair_lanes * 4) + (lane % pair_lanes) * 4);
         const float4 a = c4[0], b = c4[1];
         cs[0] = make_float2(a.x, a.y); cs[1] = make_float2(a.z, a.w);
         cs[2] = make_float2(b.x, b.y); cs[3] = make_float2(b.z, b.w);
@@ -133,12 +143,20 @@ __device__ __forceinline__ void project_head(const Projections& pj, const float*
         for (int j = 0; j < 4; ++j) v[j] = v[j] * inv * wj[j];
     }
     if (rotate) {
-        // dimension i < 64 pairs with i + 64: lanes 0-15 hold x_i, lanes 16-31 the partners
+        // the whole head: dimension i < 64 pairs with i + 64, lanes 0-15 hold x_i, lanes 16-31 the partners
+        const bool turns = lane < 2 * pair_lanes, first = lane < pair_lanes;
+        const int partner = first ? lane + pair_lanes : (turns ? lane - pair_lanes : lane);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-            v[j] = lane < 16 ? v[j] * cs[j].x - other * cs[j].y : other * cs[j].y + v[j] * cs[j].x;
+            const float other = __shfl_sync(0xffffffffu, v[j], partner);
+            if (turns) v[j] = first ? v[j] * cs[j].x - other * cs[j].y : other * cs[j].y + v[j] * cs[j].x;
         }
+    }
+    if (what != 2 && pj.post_norm) {
+        const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+        const float inv = rsqrtf(ss / 128.f + pj.eps);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] *= inv;
     }
 }
 __device__ __forceinline__ uint2 pack4_bf16(const float* v) {
@@ -321,6 +339,16 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                     const bool is_k = warp == WARPS - 2;
                     const int head = is_k ? nq + kvh : nq + nkv + kvh;
                     project_head(pj, row + (size_t)head * HD + lane * 4, is_k ? 1 : 2, t, lane, share, v);
+                    if (!is_k && (pj.v_keep || pj.v_first)) {
+                        const size_t vrow = ((size_t)t * nkv + kvh) * HD + lane * 4;
+                        if (pj.v_keep) *reinterpret_cast<float4*>(pj.v_keep + vrow) = make_float4(v[0], v[1], v[2], v[3]);
+                        if (pj.v_first) {
+                            const float lam = pj.v_lambda[0];
+                            const float4 f = *reinterpret_cast<const float4*>(pj.v_first + vrow);
+                            v[0] = (1.f - lam) * v[0] + lam * f.x; v[1] = (1.f - lam) * v[1] + lam * f.y;
+                            v[2] = (1.f - lam) * v[2] + lam * f.z; v[3] = (1.f - lam) * v[3] + lam * f.w;
+                        }
+                    }
                     __nv_bfloat16* dst = (is_k ? pj.k_out : pj.v_out) +
                                          (((size_t)page * nkv + kvh) * RB_PAGE + (pos % RB_PAGE)) * HD;
                     *reinterpret_cast<uint2*>(dst + lane * 4) = pack4_bf16(v);
@@ -825,6 +853,8 @@ extern "C" int rb_attention_decode(const void* q, int q_stride, const void* k_ca
 // and writes the new token's key and value into the cache (write_kv != 0) before reading it.
 // With row_sumsq (shares [row_groups][>= T] of the sums of squares of the rows the projection was made
 // from, over row_width values each) the sums are first scaled by rsqrt(sum / row_width + row_eps).
+// keep, sink and gate as in rb_attention_decode; rot_dim, post_norm, v_first, v_lambda, v_keep: see Projections (the rows
+// may be wider than the heads they hold: gate columns follow the values).
 // Returns RB_ERR_BAD_SIZE for other head sizes, RB_ERR_BAD_ALIGN for partial sums off 16 bytes.
 extern "C" int rb_attention_decode_fused(const float* proj, int n_in, long long in_stride, int row_stride,
                                          const void* q_norm_w, const void* k_norm_w, int w_f32, float eps,
@@ -834,9 +864,16 @@ extern "C" int rb_attention_decode_fused(const float* proj, int n_in, long long 
                                          const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                                          const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
                                          int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
-                                         int* counters, void* out, int o_stride, void* stream) {
+                                         int* counters, void* out, int o_stride, int keep, float sink, int rot_dim,
+                                         int post_norm, const float* v_first, const float* v_lambda, float* v_keep,
+                                         const void* gate, int gate_f32, int gate_n_in, long long gate_in_stride,
+                                         long long gate_row_stride, void* stream) {
     if (hd != 128 || proj == nullptr || n_in < 1) return RB_ERR_BAD_SIZE;
-    if (((uintptr_t)proj & 15) || (in_stride % 4) || (row_stride % 4) || ((uintptr_t)cos_sin & 7)) return RB_ERR_BAD_ALIGN;
+    if (((uintptr_t)proj & 15) || (in_stride % 4) || (row_stride % 4) || ((uintptr_t)cos_sin & 15)) return RB_ERR_BAD_ALIGN;
+    if (rot_dim <= 0) rot_dim = 128;
+    if (rot_dim > 128 || rot_dim % 8 || (v_first && !v_lambda) || ((v_first || v_keep) && !write_kv) || (gate && gate_n_in < 1))
+        return RB_ERR_BAD_SIZE;
+    if (((uintptr_t)v_first & 15) || ((uintptr_t)v_keep & 15)) return RB_ERR_BAD_ALIGN;
     if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return RB_ERR_BAD_SIZE;
     Projections pj = {};
     pj.proj = proj; pj.n_in = n_in; pj.in_stride = in_stride; pj.row_stride = row_stride;
@@ -848,8 +885,11 @@ extern "C" int rb_attention_decode_fused(const float* proj, int n_in, long long 
     pj.row_sumsq = row_sumsq; pj.row_groups = row_groups; pj.row_sumsq_ld = row_sumsq_ld;
     pj.row_eps = row_eps; pj.row_inv_width = row_width > 0 ? 1.f / (float)row_width : 0.f;
     if (row_sumsq != nullptr && (row_groups < 1 || row_width < 1)) return RB_ERR_BAD_SIZE;
+    pj.rot_dim = rot_dim; pj.post_norm = post_norm;
+    pj.v_first = v_first; pj.v_lambda = v_lambda; pj.v_keep = v_keep;
+    if (gate != nullptr) pj.gate = GateCols{gate, gate_f32, gate_n_in, gate_in_stride, gate_row_stride};
     return decode_entry(nullptr, 0, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, nkv, hd,
-                        scale, window, 0, RB_NO_SINK, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, pj, stream);
+                        scale, window, keep, sink, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, pj, stream);
 }
 
 // ---- the same kernel for callers that cannot allocate (see no_alloc.h) -----------------------------

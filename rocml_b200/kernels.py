@@ -146,7 +146,8 @@ def _lib():
                                             _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _ll, _ll, _vp]
         lib.rb_attention_decode_fused.argtypes = [_vp, _i, _ll, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _i, _ll, _f, _i,
                                                   _vp, _vp, _vp, _i, _vp, _vp,
-                                                  _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]
+                                                  _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp, _vp, _i,
+                                                  _i, _f, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _ll, _ll, _vp]
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_add.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]
@@ -580,7 +581,10 @@ def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch
                            k_norm_w: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor],
                            write_kv: bool, scale: float, window: int, n_chunks: int,
                            part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
-                           pages_per_block: int = 1, rowscale=None, row_width: int = 0) -> bool:
+                           pages_per_block: int = 1, rowscale=None, row_width: int = 0, keep: int = 0,
+                           sink: Optional[float] = None, rot_dim: int = 0, post_norm: bool = False,
+                           v_first: Optional[torch.Tensor] = None, v_lambda: Optional[torch.Tensor] = None,
+                           v_keep: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> bool:
     """attention_decode for head size 128 that takes the step's projections as the matrix product left
     them: ``proj`` float32 [S, T, (nq + 2 nkv) * 128] partial sums (or [T, ...]; only the nq query heads
     when ``write_kv`` is off).  The kernel adds them, applies the per-head norm and the rotation
@@ -588,14 +592,33 @@ def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch
     value into its page before reading it: the work of qk_norm_rope_cache, without a kernel in between.
     ``rowscale`` = (sumsq float32 [G, >= T], eps) with ``row_width``: the rows the projection was made
     from were residual * norm weight; the sums are scaled by rsqrt(sum / row_width + eps) first.
+    ``keep``, ``sink`` and ``gate`` as in attention_decode.  ``rot_dim`` (0: the whole head): only the first
+    rot_dim dimensions of a head turn and ``cos_sin`` is [T, rot_dim / 2, 2]; ``post_norm``: queries and keys are divided
+    by their root mean square after the rotation; ``v_keep``: float32 [T, nkv * 128], receives the new values as projected;
+    ``v_first`` and ``v_lambda`` (float32 [1]): such rows of an earlier layer, blended into what is cached.  With any
+    of these the rows may hold further columns after the heads.
     Returns False when the kernel does not take the sizes (use the two kernels)."""
     if hd != 128 or proj.dtype != torch.float32 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 \
             or out.stride(-1) != 1 or n_seqs * nq > _COUNTER_INTS:
         return False
     width = (nq + (2 * nkv if write_kv else 0)) * hd
     n_in, in_stride, row_stride = _partials(proj, "attention_decode_fused")
-    if proj.shape[-1] != width:
+    if proj.shape[-1] != width and (gate is None or proj.shape[-1] < width):
         raise KernelError(f"attention_decode_fused: projections must be {width} wide")
+    rot = int(rot_dim) or hd
+    if rot % 8 or rot > hd:
+        return False
+    for name, t in (("v_first", v_first), ("v_keep", v_keep)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.numel() < n_seqs * nkv * hd):
+            raise KernelError(f"attention_decode_fused: {name} must be contiguous float32 [T, nkv * 128]")
+    if v_first is not None and (v_lambda is None or v_lambda.dtype != torch.float32):
+        raise KernelError("attention_decode_fused: v_first needs v_lambda, float32 [1]")
+    g_n, g_in, g_row = 0, 0, 0
+    if gate is not None:
+        if gate.dtype not in (torch.bfloat16, torch.float32) or gate.dim() not in (2, 3) or gate.stride(-1) != 1 or \
+                gate.shape[-1] != nq * hd:
+            return False
+        g_n, g_in, g_row = (gate.shape[0], gate.stride(0), gate.stride(1)) if gate.dim() == 3 else (1, 0, gate.stride(0))
     if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
         raise KernelError("attention_decode_fused: cache must be [pages, nkv, 64, hd]")
     if (q_norm_w is None) != (k_norm_w is None):
@@ -605,8 +628,8 @@ def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch
         if q_norm_w.dtype != k_norm_w.dtype or q_norm_w.numel() != hd or k_norm_w.numel() != hd:
             raise KernelError("attention_decode_fused: norm weights must share a type and be [head_dim]")
         w_f32 = 1 if q_norm_w.dtype == torch.float32 else 0
-    if cos_sin is not None and (cos_sin.dtype != torch.float32 or cos_sin.numel() < n_seqs * hd):
-        raise KernelError("attention_decode_fused: cos_sin must be float32 [T, 64, 2]")
+    if cos_sin is not None and (cos_sin.dtype != torch.float32 or cos_sin.numel() < n_seqs * rot):
+        raise KernelError("attention_decode_fused: cos_sin must be float32 [T, rot_dim / 2, 2]")
     _check_parts(part_acc, part_ml, n_chunks, "attention_decode_fused")
     rc = _lib().rb_attention_decode_fused(
         _ptr(proj), n_in, in_stride, row_stride, _ptr(q_norm_w), _ptr(k_norm_w), w_f32, float(eps), _ptr(cos_sin),
@@ -614,7 +637,9 @@ def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch
         _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"), block_table.shape[1],
         _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs, nq, nkv, hd, float(scale),
         int(window), int(n_chunks), int(pages_per_block), _ptr(part_acc), _ptr(part_ml),
-        _ptr(decode_counters(out.device)), _ptr(out), out.stride(0), _stream())
+        _ptr(decode_counters(out.device)), _ptr(out), out.stride(0), int(keep), _sink(sink), rot, 1 if post_norm else 0,
+        _ptr(v_first), _ptr(v_lambda), _ptr(v_keep), _ptr(gate), 1 if gate is not None and gate.dtype == torch.float32 else 0,
+        g_n, g_in, g_row, _stream())
     if rc in (10001, 10003):
         return False
     _check(rc, "attention_decode_fused")

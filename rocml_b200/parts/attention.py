@@ -235,8 +235,6 @@ class Attention(Mixer):
         if isinstance(xn, DeferredNorm):
             xn = xn.materialize()
         proj = self.qkv.forward_auto(xn, T)
-        q = torch.empty((T, self.nq * self.hdp), dtype=act, device=dev)
-        gates = torch.empty((T, self.nq), dtype=torch.float32, device=dev) if self.gated and not self.gate_per_value else None
         # values blended across layers: the source layer leaves its own for the step's later layers
         v_out = v_first = None
         if self.value_mix == "source":
@@ -246,6 +244,20 @@ class Attention(Mixer):
             if v_first is None or v_first.shape != (T, self.nkv * self.vd):
                 raise ConfigError("attention: a layer blends its values with a source layer's, which must run before it "
                                   "in the same step with the same key/value heads and value size")
+        # a raw gate for every value of heads that carry no padding: an attention kernel that takes the projection's gate
+        # columns multiplies its result by their sigmoid as it writes it
+        raw_gate = None
+        if self.gate_per_value and self.hdp == self.vd:
+            off = self.nq * self.hd + self.nkv * (self.hd + self.vd)
+            raw_gate = proj[..., off:off + self.nq * self.vd]
+        # one token a sequence, heads of 128 on both sides: the attention kernel makes the heads from the projection's
+        # partial sums itself (norm, partial rotation, division by the root mean square, blended values, the cache write)
+        if batch.is_decode and writes and self.hd == self.vd == self.hdp and (raw_gate is not None or not self.gated):
+            attn = torch.empty((T, self.nq * self.hd), dtype=act, device=dev)
+            if self._decode_fused(proj, attn, batch, view, window, writes, v_first=v_first, v_keep=v_out, gate=raw_gate):
+                return self._project_out(attn, T, sink, add_into)
+        q = torch.empty((T, self.nq * self.hdp), dtype=act, device=dev)
+        gates = torch.empty((T, self.nq), dtype=torch.float32, device=dev) if self.gated and not self.gate_per_value else None
         with scope(op="rotate_cache"):
             kernels.qk_norm_rope_cache(
                 proj, q, T, self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
@@ -255,12 +267,6 @@ class Attention(Mixer):
                 gates=gates, post_norm=self.qk_unit_norm, v_first=v_first, v_lambda=self.v_lambda if v_first is not None else None,
                 v_out=v_out)
         attn = torch.empty((T, self.nq * self.hdp), dtype=act, device=dev)
-        # a gate for every value of heads that carry no padding: the attention kernel that takes the projection's gate
-        # columns multiplies its result by their sigmoid as it writes it
-        raw_gate = None
-        if self.gate_per_value and self.hdp == self.vd:
-            off = self.nq * self.hd + self.nkv * (self.hd + self.vd)
-            raw_gate = proj[..., off:off + self.nq * self.vd]
         gated_inside = paged_attention(q, attn, batch, view.k, view.v, view.block_table, self.nq, self.nkv, self.hdp, self.scale,
                                        window, keep=self.keep_first, sink=self.sink, gate=raw_gate)
         if (self.gated and not gated_inside) or self.hdp != self.vd:
@@ -272,6 +278,9 @@ class Attention(Mixer):
             with scope(op="head_gate"):
                 kernels.head_gate(attn, narrow, gates, self.nq, self.hdp, self.vd, T, raw=raw, per_value=self.gate_per_value)
             attn = narrow
+        return self._project_out(attn, T, sink, add_into)
+
+    def _project_out(self, attn, T, sink, add_into):
         if sink is not None:
             deferred = self.o.forward_residual(attn, T, sink)
             if deferred is not None:
@@ -304,18 +313,22 @@ class Attention(Mixer):
         self.attend(q, out, batch, view, window)
         return True
 
-    def _decode_fused(self, proj, out, batch, view, window, writes, rowscale=None, row_width=0) -> bool:
+    def _decode_fused(self, proj, out, batch, view, window, writes, rowscale=None, row_width=0, v_first=None, v_keep=None,
+                      gate=None) -> bool:
         """One token per sequence, head size 128, float32 projections: the attention kernel itself
         adds the partial sums, normalises and rotates the queries and writes the new key and value,
         so no kernel stands between the projection and the attention.  False: not this time."""
         if self.hd != 128 or proj.dtype != torch.float32 or view.k.dtype != torch.bfloat16:
             return False
         rot = self.position.rot_dim if self.position.inv_freq is not None else 0
-        if rot not in (0, self.hd):
+        if rot % 8 or getattr(self.position, "interleaved", False) or (writes and self.nq // self.nkv > 16):
             return False
         n_pages = max(1, (batch.max_kv_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
         groups = self.nkv * ((self.nq // self.nkv + 15) // 16)
         n_blocks, ppb = kernels.decode_split(batch.n_seqs, groups, n_pages, out.device)
+        if self.keep_first and ppb == 0:         # kept first keys: a sequence takes whole blocks (see paged_attention)
+            ppb = -(-n_pages // min(n_pages, kernels.DECODE_CLUSTER_MAX))
+            n_blocks = -(-n_pages // ppb)
         acc = ml = None
         if n_pages > 1:
             T = batch.n_tokens
@@ -326,7 +339,9 @@ class Attention(Mixer):
             proj, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q, batch.kv_len, batch.n_seqs,
             self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
             self.position.cos_sin(batch) if rot else None, writes, self.scale, window, n_blocks, acc, ml, ppb,
-            rowscale=rowscale, row_width=row_width)
+            rowscale=rowscale, row_width=row_width, keep=self.keep_first, sink=self.sink, rot_dim=rot,
+            post_norm=self.qk_unit_norm, v_first=v_first, v_lambda=self.v_lambda if v_first is not None else None,
+            v_keep=v_keep, gate=gate)
 
     def attend(self, q, out, batch, view, window):
         """Softmax attention of the step's queries over the cache (see ``paged_attention``)."""

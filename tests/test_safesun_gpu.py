@@ -232,6 +232,96 @@ def test_attention_with_kept_first_positions_and_one_more_term(case, dtype):
             assert (_plain_attention(qs, ks, vs, scale, window, keep + 1, sink) - want).abs().max() > 0.1
 
 
+@pytest.mark.parametrize("lens, nq, nkv, window, keep, sink, rot_dims, order, parts, mix", [
+    ([1, 70, 333, 700], 8, 2, 150, 3, True, 32, "rotate_then_unit", 3, "source"),
+    ([64, 65, 1100], 4, 4, 300, 100, False, 128, "norm_then_rotate", 8, "mix"),
+    ([129, 5], 16, 1, 40, 0, True, 0, "rotate_then_unit", 1, None),
+    ([2000, 900, 31, 64, 640], 6, 3, 64, 64, True, 72, "norm_then_rotate", 2, "mix"),
+])
+def test_single_tokens_made_from_partial_sums_inside_the_attention_kernel(lens, nq, nkv, window, keep, sink, rot_dims, order, parts, mix):
+    """Heads of 128, one token a sequence: the decode kernel adds the projection's partial sums, normalises, turns part
+    of each head, divides by the root mean square, keeps or blends the new values, writes key and value to their page,
+    attends under the window with kept first positions and one more term, and multiplies by the sigmoid of the gate
+    columns.  Against the plain implementation; the new key is made to matter (the query looks for it)."""
+    from rocml_b200 import kernels
+    from test_kernels_gpu import paged_case
+    hd, eps, B = 128, 1e-5, len(lens)
+    dt = torch.bfloat16
+    ks, vs, qs, kc, vc, meta = paged_case(7 + len(lens), lens, [1] * B, nq, nkv, hd, dt)
+    g = torch.Generator().manual_seed(nq)
+    width = (nq + 2 * nkv) * hd
+    total = width + nq * hd + 8                       # heads, gate columns, padding
+    x = torch.randn(B, total, generator=g)
+    for b in range(B):                                # each sequence's first query head resembles its new key
+        x[b, :hd] = x[b, nq * hd:nq * hd + hd] * 1.5
+    rows = torch.randn(parts, B, total, generator=g)
+    rows[0] += x - rows.sum(0)                        # partial sums whose sum is x up to 32-bit rounding
+    x = rows.double().sum(0)
+    pos = [n - 1 for n in lens]
+    rot = {"base": 10000.0, "dims": rot_dims, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}}
+    inv = mag = cs = None
+    if rot_dims:
+        f, mag = P.frequencies(rot)
+        inv = f.float().to(DEV)
+        cs = kernels.rope_table(torch.tensor(pos, dtype=torch.int32, device=DEV), inv, B, mag)
+    wq = wk = None
+    if order == "norm_then_rotate":
+        wq, wk = (1 + 0.3 * torch.randn(hd, generator=g)).to(dt).to(DEV), (1 + 0.3 * torch.randn(hd, generator=g)).to(dt).to(DEV)
+    xq = x[:, :nq * hd].reshape(B, nq, hd)
+    xk = x[:, nq * hd:(nq + nkv) * hd].reshape(B, nkv, hd)
+    xv = x[:, (nq + nkv) * hd:width].reshape(B, nkv, hd)
+    z = x[:, width:width + nq * hd].reshape(B, nq, hd)
+    if order == "norm_then_rotate":
+        xq, xk = P.rms(xq, eps) * wq.cpu().double(), P.rms(xk, eps) * wk.cpu().double()
+    if rot_dims:
+        xq, xk = P.rotate_half(xq, pos, rot), P.rotate_half(xk, pos, rot)
+    if order == "rotate_then_unit":
+        xq, xk = P.rms(xq, eps), P.rms(xk, eps)
+    v_first = lam = v_keep = None
+    v_new = xv
+    if mix == "mix":
+        v_first = torch.randn(B, nkv * hd, generator=g)
+        lam = torch.tensor([0.6], dtype=torch.float32)
+        v_new = P.mix_values(xv, v_first.double().reshape(B, nkv, hd), 0.6)
+    elif mix == "source":
+        v_keep = torch.full((B, nkv * hd), 9.0, dtype=torch.float32, device=DEV)
+    scale = 0.09
+    want = []
+    for b in range(B):
+        k = torch.cat([ks[b][:-1].double(), xk[b:b + 1].to(dt).double()])
+        v = torch.cat([vs[b][:-1].double(), v_new[b:b + 1].to(dt).double()])
+        want.append(_plain_attention([xq[b:b + 1]], [k], [v], scale, window, keep, sink))
+    want = torch.cat(want, 0) * torch.sigmoid(z)
+    d = {k: v.to(DEV) for k, v in meta.items()}
+    kc, vc = kc.to(DEV), vc.to(DEV)
+    n_pages = (max(lens) + 63) // 64
+    out = torch.full((B, nq * hd), float("nan"), dtype=dt, device=DEV)
+    for ppb in ([1, 4] if n_pages > 1 else [1]):
+        n_blocks = -(-n_pages // ppb)
+        acc = torch.empty((B, nq, n_blocks, hd), dtype=torch.float32, device=DEV) if n_blocks > 1 else None
+        ml = torch.empty((B, nq, n_blocks, 2), dtype=torch.float32, device=DEV) if n_blocks > 1 else None
+        dev_rows = rows.to(DEV) if parts > 1 else rows[0].to(DEV)
+        done = kernels.attention_decode_fused(
+            dev_rows, out, kc, vc, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"], B, nq, nkv, hd, wq, wk, eps, cs, True,
+            scale, window, n_blocks, acc, ml, ppb, keep=keep, sink=0.0 if sink else None, rot_dim=rot_dims,
+            post_norm=order == "rotate_then_unit", v_first=None if v_first is None else v_first.to(DEV),
+            v_lambda=None if lam is None else lam.to(DEV), v_keep=v_keep, gate=dev_rows[..., width:width + nq * hd])
+        assert done
+        err = (out.cpu().double().reshape(want.shape) - want).abs().max().item()
+        assert err < 2e-2, (ppb, err)
+        for b in range(B):
+            page = int(meta["table"][meta["seq_slot"][b], pos[b] // 64])
+            assert close(kc[page, :, pos[b] % 64], xk[b], 1e-2) and close(vc[page, :, pos[b] % 64], v_new[b], 1e-2)
+        if v_keep is not None:
+            assert close(v_keep.reshape(B, nkv, hd), xv, 1e-6)
+    # the new key matters: without it the first head's result moves
+    b = max(range(B), key=lambda i: lens[i])
+    k = torch.cat([ks[b][:-1].double(), torch.zeros(1, nkv, hd, dtype=torch.float64)])
+    v = torch.cat([vs[b][:-1].double(), v_new[b:b + 1].double()])
+    other = _plain_attention([xq[b:b + 1]], [k], [v], scale, window, keep, sink) * torch.sigmoid(z[b:b + 1])
+    assert (other[:, 0] - want[b:b + 1, 0]).abs().max() > 0.05
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads, in_w, out_w, parts", [(3, 32, 28, 1), (8, 64, 48, 2), (2, 128, 128, 1), (5, 16, 13, 3)])
 def test_gate_for_every_value(dtype, heads, in_w, out_w, parts):

@@ -11,7 +11,8 @@ int rb_embedding(const int* ids, const void* table, int table_dtype, float* out,
 
 int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, long long delta_stride, const void* w,
                    int w_dtype, void* out, int out_dtype, const int* rows, int n_rows, int H, float eps,
-                   int write_back, const void* w2, void* out2, void* stream);
+                   int write_back, const void* w2, void* out2, const float* delta_b, int n_delta_b,
+                   long long delta_b_stride, void* stream);
 
 int rb_silu_mul(const void* in, int in_dtype, int n_in, long long in_stride, void* out, int out_dtype, int rows,
                 int I, int paired, void* stream);

@@ -69,7 +69,8 @@ extern "C" int rb_embedding(const int* ids, const void* table, int table_dtype, 
 }
 
 // ---- fused residual add + RMSNorm ---------------------------------------------------------
-// r = resid[row] + sum_s delta[s][row]   (s in fixed order, so the sum never depends on the batch)
+// r = resid[row] + sum_s delta[s][row] (+ sum_s delta_b[s][row])   (s in fixed order, first all of delta, then all of
+// delta_b, so the sum never depends on the batch and equals adding the two groups one after the other)
 // if write_back: resid[row] = r
 // out[i] = r * rsqrt(mean(r^2) + eps) * w      (and out2[i] = the same row times w2, when a second weight is given:
 //                                               two norms of one row that differ in their weights only)
@@ -98,7 +99,8 @@ template <typename OT, typename WT>
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ delta,
                                    int n_delta, size_t delta_stride, const WT* __restrict__ w,
                                    OT* __restrict__ out, const int* __restrict__ rows, int H,
-                                   float eps, int write_back, const WT* __restrict__ w2, OT* __restrict__ out2) {
+                                   float eps, int write_back, const WT* __restrict__ w2, OT* __restrict__ out2,
+                                   const float* __restrict__ delta_b, int n_delta_b, size_t delta_b_stride) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float row_buf[];  // H floats (padded to 4) + 33 for the reduction
@@ -108,24 +110,29 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ r
     if (row < 0) return;  // a padded entry
     float* r = resid + (size_t)row * H;
     float ss = 0.f;
-    const bool vec = (H & 3) == 0 && (delta_stride & 3) == 0 && (((uintptr_t)resid | (uintptr_t)delta) & 15) == 0;
+    const bool vec = (H & 3) == 0 && ((delta_stride | delta_b_stride) & 3) == 0 &&
+                     (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)delta_b) & 15) == 0;
     if (vec) {
         const int H4 = H >> 2;
         float4* rb4 = reinterpret_cast<float4*>(row_buf);
         const float4* r4 = reinterpret_cast<const float4*>(r);
         for (int i = threadIdx.x; i < H4; i += blockDim.x) {
             float4 v = r4[i];
-            const float4* d4 = reinterpret_cast<const float4*>(delta + (size_t)row * H) + i;
-            const size_t ds4 = delta_stride >> 2;
-            // eight partial sums at a time: every load is issued before the first addition, and the
-            // additions keep the partial sums' order (an absent one adds zero)
-            for (int s = 0; s < n_delta; s += 8) {
-                float4 d[8];
+            // the first group of partial sums, then the second (a layer's two sublayers), each in its order
+            for (int part = 0; part < 2; ++part) {
+                const int nd = part ? n_delta_b : n_delta;
+                const float4* d4 = reinterpret_cast<const float4*>((part ? delta_b : delta) + (size_t)row * H) + i;
+                const size_t ds4 = (part ? delta_b_stride : delta_stride) >> 2;
+                // eight partial sums at a time: every load is issued before the first addition, and the
+                // additions keep the partial sums' order (an absent one adds zero)
+                for (int s = 0; s < nd; s += 8) {
+                    float4 d[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    d[j] = s + j < n_delta ? d4[(size_t)(s + j) * ds4] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int j = 0; j < 8; ++j)
+                        d[j] = s + j < nd ? d4[(size_t)(s + j) * ds4] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) { v.x += d[j].x; v.y += d[j].y; v.z += d[j].z; v.w += d[j].w; }
+                    for (int j = 0; j < 8; ++j) { v.x += d[j].x; v.y += d[j].y; v.z += d[j].z; v.w += d[j].w; }
+                }
             }
             rb4[i] = v;
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -134,6 +141,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ r
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
             float v = r[i];
             for (int s = 0; s < n_delta; ++s) v += delta[(size_t)s * delta_stride + (size_t)row * H + i];
+            for (int s = 0; s < n_delta_b; ++s) v += delta_b[(size_t)s * delta_b_stride + (size_t)row * H + i];
             row_buf[i] = v;
             ss += v * v;
         }
@@ -176,7 +184,8 @@ __global__ void __launch_bounds__(THREADS) add_rmsnorm_rows_kernel(float* __rest
                                                                    const WT* __restrict__ w, OT* __restrict__ out,
                                                                    const int* __restrict__ rows, int H, float eps,
                                                                    int write_back, const WT* __restrict__ w2,
-                                                                   OT* __restrict__ out2) {
+                                                                   OT* __restrict__ out2, const float* __restrict__ delta_b,
+                                                                   int n_delta_b, size_t delta_b_stride) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[33];
@@ -191,21 +200,26 @@ __global__ void __launch_bounds__(THREADS) add_rmsnorm_rows_kernel(float* __rest
         const int i = threadIdx.x + j * THREADS;
         v[j] = i < H4 ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    for (int s = 0; s < n_delta; s += 2) {                  // partial sums in their order, two in flight
-        const float4* d4 = reinterpret_cast<const float4*>(delta + (size_t)s * delta_stride + (size_t)row * H);
-        const float4* e4 = reinterpret_cast<const float4*>(delta + (size_t)(s + 1) * delta_stride + (size_t)row * H);
-        const bool second = s + 1 < n_delta;
-        float4 d[8], e[8];
+    for (int part = 0; part < 2; ++part) {                      // the first group of partial sums, then the second
+        const float* dp = part ? delta_b : delta;
+        const int nd = part ? n_delta_b : n_delta;
+        const size_t dst = part ? delta_b_stride : delta_stride;
+        for (int s = 0; s < nd; s += 2) {                       // partial sums in their order, two in flight
+            const float4* d4 = reinterpret_cast<const float4*>(dp + (size_t)s * dst + (size_t)row * H);
+            const float4* e4 = reinterpret_cast<const float4*>(dp + (size_t)(s + 1) * dst + (size_t)row * H);
+            const bool second = s + 1 < nd;
+            float4 d[8], e[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int i = threadIdx.x + j * THREADS;
-            d[j] = i < H4 ? d4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-            e[j] = second && i < H4 ? e4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < 8; ++j) {
+                const int i = threadIdx.x + j * THREADS;
+                d[j] = i < H4 ? d4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                e[j] = second && i < H4 ? e4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { v[j].x += d[j].x; v[j].y += d[j].y; v[j].z += d[j].z; v[j].w += d[j].w; }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { v[j].x += e[j].x; v[j].y += e[j].y; v[j].z += e[j].z; v[j].w += e[j].w; }
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { v[j].x += d[j].x; v[j].y += d[j].y; v[j].z += d[j].z; v[j].w += d[j].w; }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { v[j].x += e[j].x; v[j].y += e[j].y; v[j].z += e[j].z; v[j].w += e[j].w; }
     }
     float ss = 0.f;
 #pragma unroll
@@ -229,20 +243,23 @@ __global__ void __launch_bounds__(THREADS) add_rmsnorm_rows_kernel(float* __rest
 template <typename OT, typename WT>
 static int launch_add_rmsnorm(float* resid, const float* delta, int n_delta, size_t delta_stride,
                               const void* w, void* out, const int* rows, int n_rows, int H, float eps,
-                              int write_back, const void* w2, void* out2, cudaStream_t s) {
+                              int write_back, const void* w2, void* out2, const float* delta_b, int n_delta_b,
+                              size_t delta_b_stride, cudaStream_t s) {
     // many rows: the register kernel, when everything is 16-byte aligned and a row fits its threads
     // (up to 256 rows are at most one wave of the kernel below, whose 1,024 threads a row finish sooner)
-    const bool aligned = (H & 3) == 0 && (delta_stride & 3) == 0 &&
-                         ((((uintptr_t)resid | (uintptr_t)delta) & 15) == 0) &&
+    const bool aligned = (H & 3) == 0 && ((delta_stride | delta_b_stride) & 3) == 0 &&
+                         ((((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)delta_b) & 15) == 0) &&
                          ((((uintptr_t)out | (uintptr_t)out2 | ((size_t)H * sizeof(OT))) & 15) == 0) &&
                          ((((uintptr_t)w | (uintptr_t)w2) & (4 * sizeof(WT) - 1)) == 0);
     if (n_rows > (H >= 4096 ? 256 : 64) && aligned && H <= 8 * 4 * 256) {
         if (H <= 8 * 4 * 128)
             RB_LAUNCH((add_rmsnorm_rows_kernel<OT, WT, 128>), dim3(n_rows), dim3(128), 0, s, resid, delta, n_delta,
-                      delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back, (const WT*)w2, (OT*)out2);
+                      delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back, (const WT*)w2, (OT*)out2, delta_b,
+                      n_delta_b, delta_b_stride);
         else
             RB_LAUNCH((add_rmsnorm_rows_kernel<OT, WT, 256>), dim3(n_rows), dim3(256), 0, s, resid, delta, n_delta,
-                      delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back, (const WT*)w2, (OT*)out2);
+                      delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back, (const WT*)w2, (OT*)out2, delta_b,
+                      n_delta_b, delta_b_stride);
         RB_LAUNCH_CHECK();
         return RB_OK;
     }
@@ -256,26 +273,30 @@ static int launch_add_rmsnorm(float* resid, const float* delta, int n_delta, siz
     // one 16-byte column group per thread where the row allows it: a row's loads are all in flight at once
     const int threads = H >= 4096 ? 1024 : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
     RB_LAUNCH((k), dim3(n_rows), dim3(threads), smem, s, resid, delta, n_delta, delta_stride, (const WT*)w, (OT*)out, rows, H,
-                                    eps, write_back, (const WT*)w2, (OT*)out2);
+                                    eps, write_back, (const WT*)w2, (OT*)out2, delta_b, n_delta_b, delta_b_stride);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }
 
 extern "C" int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, long long delta_stride,
                               const void* w, int w_dtype, void* out, int out_dtype, const int* rows,
-                              int n_rows, int H, float eps, int write_back, const void* w2, void* out2, void* stream) {
+                              int n_rows, int H, float eps, int write_back, const void* w2, void* out2,
+                              const float* delta_b, int n_delta_b, long long delta_b_stride, void* stream) {
     if (n_rows <= 0) return RB_OK;
     if ((w2 == nullptr) != (out2 == nullptr)) return RB_ERR_BAD_SIZE;
+    if (delta_b == nullptr) n_delta_b = 0;
+    if (n_delta_b == 0) { delta_b = nullptr; delta_b_stride = 0; }
     cudaStream_t s = (cudaStream_t)stream;
     const size_t ds = (size_t)delta_stride;
+    const size_t dbs = (size_t)delta_b_stride;
     if (out_dtype == RB_BF16 && w_dtype == RB_BF16)
-        return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, s);
+        return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, delta_b, n_delta_b, dbs, s);
     if (out_dtype == RB_BF16 && w_dtype == RB_F32)
-        return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, s);
+        return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, delta_b, n_delta_b, dbs, s);
     if (out_dtype == RB_F32 && w_dtype == RB_BF16)
-        return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, s);
+        return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, delta_b, n_delta_b, dbs, s);
     if (out_dtype == RB_F32 && w_dtype == RB_F32)
-        return launch_add_rmsnorm<float, float>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, s);
+        return launch_add_rmsnorm<float, float>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, w2, out2, delta_b, n_delta_b, dbs, s);
     return RB_ERR_BAD_DTYPE;
 }
 

@@ -193,6 +193,9 @@ class Model:
             if e.add_input or e.add_row is not None:
                 # what the layer before left pending joins the stream first, then the embedding output, then the row
                 with scope(layer=i, op="stream_additions"):
+                    if isinstance(pending, (tuple, list)):          # a pair of results: the first joins alone
+                        kernels.residual_inject(resid, pending[0])
+                        pending = pending[1]
                     delta = pending if isinstance(pending, torch.Tensor) else None
                     vec = self.added[e.add_row[0]][e.add_row[1]] if e.add_row is not None else None
                     kernels.residual_inject(resid, delta, x0 if e.add_input else None, vec)

@@ -126,7 +126,7 @@ def _lib():
     lib = library()
     if not _sigs_done:
         lib.rb_embedding.argtypes = [_vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp]
-        lib.rb_add_rmsnorm.argtypes = [_vp, _vp, _i, _ll, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _vp, _vp, _vp]
+        lib.rb_add_rmsnorm.argtypes = [_vp, _vp, _i, _ll, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _vp, _vp, _vp, _i, _ll, _vp]
         lib.rb_silu_mul.argtypes = [_vp, _i, _i, _ll, _vp, _i, _i, _i, _i, _vp]
         lib.rb_cast.argtypes = [_vp, _i, _vp, _i, _ll, _vp]
         lib.rb_qk_norm_rope_cache.argtypes = [_vp, _i, _i, _ll, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f,
@@ -203,14 +203,25 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status:
 
 # ---- fused residual add + RMSNorm ---------------------------------------------------------------
 
+def _n_partials(delta) -> int:
+    """How many partial sums a delta (None, [S, T, H], or a pair of such) brings."""
+    if delta is None:
+        return 0
+    if isinstance(delta, (tuple, list)):
+        return sum(d.shape[0] for d in delta if d is not None)
+    return delta.shape[0]
+
+
 @_profiled(lambda a, facts: _cost.add_norm(
     a["n_rows"] if a["n_rows"] is not None else (a["rows"].numel() if a["rows"] is not None else a["resid"].shape[0]),
-    a["resid"].shape[1], a["delta"].shape[0] if a["delta"] is not None else 0, _esz(a["out"]),
+    a["resid"].shape[1], _n_partials(a["delta"]), _esz(a["out"]),
     bool(a["write_back"]) and a["delta"] is not None, _esz(a["weight"])))
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
                 write_back: bool = True, weight2: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None):
     """resid [T, H] float32 (+= sum of delta [S, T, H] float32); out[i] = rmsnorm(row) * weight.
+    ``delta`` may also be a pair of such tensors (the results of a layer's two sublayers): the first one's partial sums
+    are added in their order, then the second one's.
 
     With ``rows`` (int32 indices, -1 = skip) output row i comes from source row rows[i].  ``weight2`` and
     ``out2`` (like ``weight`` and ``out``): a second norm of the same rows with the same eps, whose output differs
@@ -218,12 +229,20 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     T, H = resid.shape
     if resid.dtype != torch.float32 or not resid.is_contiguous() or not out.is_contiguous():
         raise KernelError("add_rmsnorm: resid must be contiguous float32, out contiguous")
-    n_delta, stride = 0, 0
-    if delta is not None:
-        if delta.dtype != torch.float32 or not delta.is_contiguous() or delta.dim() != 3 or \
-                delta.shape[1] < T or delta.shape[2] != H:
+    delta_b = None
+    if isinstance(delta, (tuple, list)):
+        delta, delta_b = delta
+    n_delta, stride, n_delta_b, stride_b = 0, 0, 0, 0
+    for d in (delta, delta_b):
+        if d is not None and (d.dtype != torch.float32 or not d.is_contiguous() or d.dim() != 3 or
+                              d.shape[1] < T or d.shape[2] != H):
             raise KernelError("add_rmsnorm: delta must be contiguous float32 [S, >=T, H]")
+    if delta is None:
+        delta, delta_b = delta_b, None
+    if delta is not None:
         n_delta, stride = delta.shape[0], delta.stride(0)
+    if delta_b is not None:
+        n_delta_b, stride_b = delta_b.shape[0], delta_b.stride(0)
     n = (rows.numel() if rows is not None else T) if n_rows is None else n_rows
     if out.shape[-1] != H or out.numel() < n * H or weight.numel() != H:
         raise KernelError("add_rmsnorm: shapes do not fit")
@@ -234,7 +253,8 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
         raise KernelError("add_rmsnorm: the second weight and output must look like the first")
     rc = _lib().rb_add_rmsnorm(_ptr(resid), _ptr(delta), n_delta, stride, _ptr(weight), dtype_code(weight.dtype),
                                _ptr(out), dtype_code(out.dtype), None if rows is None else _i32(rows, "rows"),
-                               n, H, float(eps), 1 if write_back else 0, _ptr(weight2), _ptr(out2), _stream())
+                               n, H, float(eps), 1 if write_back else 0, _ptr(weight2), _ptr(out2), _ptr(delta_b), n_delta_b,
+                               stride_b, _stream())
     _check(rc, "add_rmsnorm")
 
 

@@ -132,8 +132,9 @@ class Part:
 
 
 class Norm(Part):
-    """forward(resid [T, H] float32, delta None | [S, T, H] float32, ...) adds the delta into the
-    residual stream in place and returns the normalised rows in the activations' type."""
+    """forward(resid [T, H] float32, delta None | [S, T, H] float32 | a pair of such, ...) adds the delta
+    (of a pair: the first, then the second) into the residual stream in place and returns the normalised
+    rows in the activations' type."""
 
     def forward(self, resid, delta, n_rows: Optional[int] = None, rows=None, write_back=True):
         raise NotImplementedError

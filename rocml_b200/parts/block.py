@@ -18,6 +18,12 @@ from .base import (BuildEnv, DeferredNorm, NormedRows, ResidualSink, RoutedRows,
 ADD_INTO_MIN_TOKENS = 256
 
 
+def _is_partial_sums(x, n_rows: int) -> bool:
+    """float32 [S, >= n_rows, H], contiguous: the form in which a norm's kernel adds a result into the stream."""
+    return isinstance(x, torch.Tensor) and x.dim() == 3 and x.dtype == torch.float32 and x.is_contiguous() \
+        and x.shape[1] >= n_rows
+
+
 @register_arrangement("pre_norm")
 class PreNormBlock:
     """x += mixer(norm1(x)); x += ff(norm2(x)) (rocml/src/forward/mod.rs:281-340).
@@ -222,9 +228,9 @@ class SandwichNormBlock:
 class ParallelBlock:
     """h = norm(x); x += mixer(h) + ff(h): one norm, and both sublayers read its output.
 
-    Both results travel as deltas (partial sums over K); the mixer's joins the 32-bit residual stream in a
-    small kernel of its own, the feed-forward's rides on to the next layer's norm (or the model's last one),
-    which adds it in the kernel that normalises.  For prompts the sublayers are offered to add into the residual
+    Both results travel as deltas (partial sums over K) and ride on, as a pair, to the next layer's norm (or the
+    model's last one), which adds the mixer's and then the feed-forward's in the kernel that normalises; a result
+    in another form joins the 32-bit residual stream in a small kernel of its own.  For prompts the sublayers are offered to add into the residual
     inside their last product instead.  A layer without a feed-forward has only the mixer."""
 
     chains = False
@@ -291,12 +297,19 @@ class ParallelBlock:
             delta = self.mixer.forward(xn, batch, view)
         if self.ff is None:
             return delta
-        if delta is not None:
-            with scope(op="mixer_add"):
-                kernels.residual_inject(resid, delta)
         if adds and getattr(self.ff, "can_add_into", False):
+            if delta is not None:
+                with scope(op="mixer_add"):
+                    kernels.residual_inject(resid, delta)
             return self.ff.forward(xf, batch, add_into=resid)
-        return self.ff.forward(xf, batch)
+        ff_delta = self.ff.forward(xf, batch)
+        if delta is None:
+            return ff_delta
+        if _is_partial_sums(delta, T) and _is_partial_sums(ff_delta, T):
+            return (delta, ff_delta)          # the next norm adds both, the mixer's first: no kernel for the sum
+        with scope(op="mixer_add"):
+            kernels.residual_inject(resid, delta)
+        return ff_delta
 
 
 @register_arrangement("parallel_two_norms")

@@ -348,6 +348,42 @@ def test_add_rmsnorm(H, T, od, wd):
     assert out2[1].abs().sum() == 0
 
 
+@pytest.mark.parametrize("H,T", [(72, 7), (1001, 5), (4096, 8), (2048, 150), (1000, 90)])
+@pytest.mark.parametrize("S1,S2", [(1, 1), (3, 9), (10, 2)])
+def test_add_rmsnorm_of_two_groups_of_partial_sums(H, T, S1, S2):
+    """A pair of results (a layer's two sublayers): the sum is exactly what adding the first group into the stream
+    and then the second gives, with one weight and with two."""
+    from rocml_b200 import kernels
+    eps = 1e-6
+    resid = rnd((T, H), 1, scale=2.0)
+    a, b = rnd((S1, T + 2, H), 2), rnd((S2, T, H), 3)          # the first has rows to spare, as a padded step's has
+    w, w2 = (1 + 0.1 * rnd((H,), 4)).to(DEV), (1 + 0.1 * rnd((H,), 5)).to(DEV)
+    one_by_one = resid.to(DEV)
+    kernels.residual_inject(one_by_one, a.to(DEV)[:, :T].contiguous())
+    want = torch.empty((T, H), dtype=torch.float32, device=DEV)
+    kernels.add_rmsnorm(one_by_one, b.to(DEV), w, eps, want)
+    together = resid.to(DEV)
+    got, got2 = torch.empty_like(want), torch.empty_like(want)
+    kernels.add_rmsnorm(together, (a.to(DEV), b.to(DEV)), w, eps, got, weight2=w2, out2=got2)
+    assert torch.equal(together, one_by_one)
+    assert torch.equal(got, want)
+    r = resid.double() + a[:, :T].double().sum(0) + b.double().sum(0)
+    plain = r * torch.rsqrt((r * r).mean(-1, keepdim=True) + eps)
+    assert (together.cpu().double() - r).abs().max() < 1e-5
+    assert ((got2.cpu().double() - plain * w2.cpu().double()).abs() / plain.abs().clamp_min(1.0)).max() < 1e-5
+    # only the second of the pair, and gathered rows without write-back
+    rows = torch.tensor([T - 1, -1, 0], dtype=torch.int32, device=DEV)
+    kept = resid.to(DEV)
+    out = torch.zeros((3, H), dtype=torch.float32, device=DEV)
+    kernels.add_rmsnorm(kept, (a.to(DEV), b.to(DEV)), w, eps, out, rows=rows, write_back=False)
+    assert torch.equal(kept.cpu(), resid)
+    assert torch.equal(out[[0, 2]], want[[T - 1, 0]]) and out[1].abs().sum() == 0
+    kernels.add_rmsnorm(kept, (None, b.to(DEV)), w, eps, out, rows=rows, write_back=False)
+    r = resid.double() + b.double().sum(0)
+    plain = (r * torch.rsqrt((r * r).mean(-1, keepdim=True) + eps) * w.cpu().double())[[T - 1, 0]]
+    assert ((out[[0, 2]].cpu().double() - plain).abs() / plain.abs().clamp_min(1.0)).max() < 1e-5
+
+
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 def test_silu_mul(dt):
     from rocml_b200 import kernels

@@ -377,7 +377,8 @@ def test_add_rmsnorm_of_two_groups_of_partial_sums(H, T, S1, S2):
     out = torch.zeros((3, H), dtype=torch.float32, device=DEV)
     kernels.add_rmsnorm(kept, (a.to(DEV), b.to(DEV)), w, eps, out, rows=rows, write_back=False)
     assert torch.equal(kept.cpu(), resid)
-    assert torch.equal(out[[0, 2]], want[[T - 1, 0]]) and out[1].abs().sum() == 0
+    # (three rows take the kernel for few rows, whose sum of squares runs in another order than the one for many)
+    assert (out[[0, 2]] - want[[T - 1, 0]]).abs().max() < 1e-5 and out[1].abs().sum() == 0
     kernels.add_rmsnorm(kept, (None, b.to(DEV)), w, eps, out, rows=rows, write_back=False)
     r = resid.double() + b.double().sum(0)
     plain = (r * torch.rsqrt((r * r).mean(-1, keepdim=True) + eps) * w.cpu().double())[[T - 1, 0]]

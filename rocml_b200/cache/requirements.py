@@ -52,3 +52,32 @@ class StateRequirement:
 
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class BundleRequirement:
+    """What a layer asks when it keeps more than one thing a sequence: ``main`` (keys and values, a state, or None)
+    and named states of fixed shape beside it (the last inputs of a short convolution, the row of the token
+    before).  The layer's view of the cache then has ``extras[name]``, a state view of its own, for each."""
+
+    main: object
+    extras: Tuple[Tuple[str, StateRequirement], ...] = ()
+
+    @staticmethod
+    def of(main, **extras) -> "BundleRequirement":
+        """``main`` may itself be a bundle: its states are kept, the new ones join them."""
+        have = ()
+        if isinstance(main, BundleRequirement):
+            main, have = main.main, main.extras
+        names = [n for n, _ in have]
+        for n in extras:
+            if n in names:
+                raise ValueError(f"two states of one layer are called {n!r}")
+        return BundleRequirement(main, tuple(have) + tuple(sorted(extras.items())))
+
+
+def simple_requirements(req):
+    """The requirements a layer's answer is made of, one by one (a bundle: its main one, then its states)."""
+    if isinstance(req, BundleRequirement):
+        return ([req.main] if req.main is not None else []) + [st for _, st in req.extras]
+    return [] if req is None else [req]

@@ -19,7 +19,7 @@ the sequence's own length (the argument of rocml/src/forward/mod.rs:224-228).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Union
 
 import numpy as np
@@ -27,7 +27,7 @@ import torch
 
 from ..errors import CacheError, CacheFull, ContextOverflow
 from .pages import FreeList
-from .requirements import KVRequirement, StateRequirement
+from .requirements import BundleRequirement, KVRequirement, StateRequirement
 
 PAGE = 64
 
@@ -198,6 +198,7 @@ class CacheView:
     group: Union[KVGroup, StateGroup, None] = None
     index: int = 0                 # the layer's place inside its group
     writes: bool = True            # False: it reads another run's cache
+    extras: Dict[str, "CacheView"] = field(default_factory=dict)   # named states beside the main one (BundleRequirement)
 
     @property
     def k(self):
@@ -216,7 +217,7 @@ class CacheView:
         return self.group.state[self.index]
 
 
-Requirement = Union[KVRequirement, StateRequirement, None]
+Requirement = Union[KVRequirement, StateRequirement, BundleRequirement, None]
 
 
 class SequenceCache:
@@ -247,7 +248,16 @@ class SequenceCache:
 
         kv_members: Dict[KVRequirement, List[int]] = {}
         st_members: Dict[StateRequirement, List[int]] = {}
+        extra_members: Dict[StateRequirement, List[tuple]] = {}       # the named states of bundles: (entry, name)
+        requirements = list(requirements)
         for i, (req, src) in enumerate(zip(requirements, reads_cache_of)):
+            if isinstance(req, BundleRequirement):
+                if src is None:
+                    for name, st in req.extras:
+                        if not isinstance(st, StateRequirement):
+                            raise CacheError(f"schedule entry {i}: the state {name!r} of a bundle must be a StateRequirement")
+                        extra_members.setdefault(st, []).append((i, name))
+                requirements[i] = req = req.main
             if src is not None:
                 continue
             if isinstance(req, KVRequirement):
@@ -271,6 +281,17 @@ class SequenceCache:
             self.state_groups.append(g)
             for j, i in enumerate(members):
                 own[i] = CacheView("state", g, j, True)
+        extras: Dict[int, Dict[str, CacheView]] = {}
+        for req, members in extra_members.items():
+            g = StateGroup(req, len(members), max_slots, device)
+            self.state_groups.append(g)
+            for j, (i, name) in enumerate(members):
+                extras.setdefault(i, {})[name] = CacheView("state", g, j, True)
+        for i, views in extras.items():
+            if i in own:
+                own[i].extras = views
+            else:
+                own[i] = CacheView("none", extras=views)
         for i, (req, src) in enumerate(zip(requirements, reads_cache_of)):
             if src is not None:
                 if src not in own:

@@ -145,6 +145,10 @@ class LayerSpec:
     ff(norm2(x)), both norms of the same x.
     arrangement "sandwich_norm": x += post1(mixer(norm1(x))); x += post2(ff(norm2(x))), with the two
     post norms given by ``mixer_post_norm`` and ``ff_post_norm``; ``feed_forward`` None leaves the second half out.
+    arrangement "post_norm": x <- norm1(alpha x + g1 * mixer(h)); x <- norm2(alpha x + g2 * ff(x)): the norm follows the
+    sum and the sublayers read the stream itself.  Its constants are ``arrangement_items``: alpha (default 1),
+    layer_scale (the vectors g1, g2 exist; default False), token_shift (h_t = x_t + (x_(t-1) - x_t) * mu with a vector mu,
+    the row before kept per sequence; default False: h = x), names (roles mixer_scale, ff_scale, shift).
     ``prefix`` is the layer's tensor-name prefix in the weight files; under it the four parts'
     tensors are named ``<prefix>.<mixer_norm_name>.weight``, ``<prefix>.<mixer_name><stem>...``,
     ``<prefix>.<ff_norm_name>.weight`` and ``<prefix>.<ff_name><stem>...`` (the defaults are the
@@ -165,6 +169,11 @@ class LayerSpec:
     ff_post_norm: Optional[NormSpec] = None
     mixer_post_norm_name: str = "post_mixer_norm"
     ff_post_norm_name: str = "post_ff_norm"
+    arrangement_items: Tuple[Tuple[str, Any], ...] = ()     # the arrangement's own constants (see above)
+
+    @property
+    def arrangement_params(self) -> dict:
+        return {k: (dict(v) if isinstance(v, tuple) and v and isinstance(v[0], tuple) else v) for k, v in self.arrangement_items}
 
 
 @dataclass(frozen=True)

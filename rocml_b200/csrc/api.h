@@ -155,7 +155,7 @@ int rb_attention_generic(const void* q, int q_stride, void* out, int o_stride, i
                          const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
                          const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv, int hd,
                          float scale, int window, int keep, float sink, int chunk, int n_chunks, float* part_acc,
-                         float* part_ml, void* stream);
+                         float* part_ml, int cross, void* stream);
 
 int rb_attention_prefill(const void* q, int q_stride, void* out, int o_stride, const void* k_cache,
                          const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
@@ -205,6 +205,48 @@ int rb_st_metadata_count(const void* handle);
 int rb_st_metadata(const void* handle, int i, const char** key, const char** value);
 int rb_st_read(void* handle, int i, void* dst, long long dst_bytes, int on_device, void* stream);
 void rb_st_close(void* handle);
+
+// A layer whose norm follows the sum (postln.cu): resid <- rmsnorm(alpha * resid + gain * sum of the delta partial sums) * w,
+// in place, 32-bit; `out` (optional) receives the rows in the activations' type.  gain may be absent (ones).
+int rb_postln(float* resid, const float* delta, int n_delta, long long delta_stride, const float* gain, const float* w,
+              float alpha, float eps, void* out, int out_dtype, const int* slot_of_token, int n_rows, int H, void* stream);
+// out[t] = x[t] + (x[t - 1] - x[t]) * mu, the row before a sequence's first coming from (and the last going to) kept[slot].
+int rb_token_shift(const float* x, const float* mu, float* kept, const int* seq_slot, const int* cu_q, int n_seqs,
+                   int max_q_len, void* out, int out_dtype, int H, void* stream);
+
+// A state-space mixer (ssm.cu).  Causal convolution over `channels` columns from col0 of the projection rows, taps
+// [channels][taps] (the last is the current token's), the inputs before a step's first token in kept[slot][taps-1][channels];
+// act 1: silu.  out float32 [T, channels].
+int rb_causal_conv(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int col0, int channels,
+                   int taps, const float* w, const float* bias, int act, float* kept, const int* seq_slot, const int* cu_q,
+                   int n_seqs, int max_q_len, float* out, int ld_out, void* stream);
+// S = exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + skip * x, dt = softplus(raw + dt_bias); x, B, C columns of u (float32),
+// raw columns of the projection rows; state float32 [slots][heads][n][p].
+int rb_ssm_scan(const float* u, int ld_u, int x_off, int b_off, int c_off, const void* raw, int raw_dtype, int n_in,
+                long long in_stride, int row_stride, int dt_off, const float* dt_bias, const float* a_log, const float* skip,
+                int heads, int groups, int n, int p, float* state, const int* seq_slot, const int* cu_q, int n_seqs,
+                float* out, int ld_out, void* stream);
+// out = rmsnorm over each of `groups` parts of (y * act(z)) * w; z columns of the projection rows; act 1 silu, 2 sigmoid.
+int rb_gate_group_norm(const float* y, int ld_y, const void* proj, int proj_dtype, int n_in, long long in_stride,
+                       int row_stride, int z_off, const float* w, float eps, int groups, int W, int gate_act, void* out,
+                       int out_dtype, int ld_out, const int* slot_of_token, int T, void* stream);
+
+// Latent attention with a query latent and a rotated key part (latent.cu).
+int rb_latent_rot_prep(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int q_rank, int rank,
+                       int rot, int n_gate, const float* wq, const float* wc, float eps, void* cq_out, int cq_stride,
+                       float* gate_out, void* cache, int dp, int act_dtype, const float* cos_sin, const int* positions,
+                       const int* slot_of_token, const int* block_table, int max_pages, int T, void* stream);
+int rb_latent_q_rot(const void* q, int q_stride, int heads, int dim, int rot, int rank, int dp, const float* cos_sin,
+                    void* folded, int f_stride, int dtype, const int* slot_of_token, int T, void* stream);
+
+// Attention with a norm over the whole q and k projections and head weights mixed after the softmax (talking_heads.cu).
+int rb_wide_norm_rope_cache(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int nq, int nkv,
+                            int hd, int vd, int hdp, const float* wq, const float* wk, float eps, const float* factor,
+                            const float* cos_sin, int rot, int neighbours, void* q_out, int q_stride, void* k_cache,
+                            void* v_cache, int act_dtype, const int* positions, const int* slot_of_token,
+                            const int* block_table, int max_pages, int T, void* stream);
+int rb_talk_mix(const void* o, int o_stride, const float* mix, void* out, int out_stride, int nq, int nkv, int hdp, int vd,
+                int dtype, const int* slot_of_token, int T, void* stream);
 
 #ifdef __cplusplus
 }

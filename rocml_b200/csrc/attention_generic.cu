@@ -48,7 +48,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ seq_slot, const int* __restrict__ cu_q,
                          const int* __restrict__ kv_len, int nq, int nkv, int hd, float scale, int window,
                          int keep, float sink, int chunk, int n_chunks, float* __restrict__ part_acc,
-                         float* __restrict__ part_ml) {
+                         float* __restrict__ part_ml, int cross) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -59,6 +59,10 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     const int b = blockIdx.z;
     const int kvh = blockIdx.y / head_chunks;
     const int hc = blockIdx.y % head_chunks;
+    // cross > 1: every query head against the values of every key/value head.  nq and nkv then count pairs:
+    // pair kvh = (key head kh, value head vh) of `cross` stored heads, read by the queries of key head kh
+    const int kh = cross > 1 ? kvh / cross : kvh, vh = cross > 1 ? kvh % cross : kvh;
+    const int n_stored = cross > 1 ? nkv / cross : nkv;
     const int qblk = blockIdx.x / n_chunks;
     const int c = blockIdx.x % n_chunks;
 
@@ -90,7 +94,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 const int qi = tok0 + r / HG, hg = hc * HG + r % HG;
                 v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (i4 < ROWS * hd4 && r < QB * HG && qi < q_len && hg < g)
-                    v[u] = load4(q + (size_t)(q0 + qi) * q_stride + (size_t)(kvh * g + hg) * hd + d4 * 4);
+                    v[u] = load4(q + (size_t)(q0 + qi) * q_stride + (size_t)(kh * g + hg) * hd + d4 * 4);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -104,7 +108,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
             const int qi = tok0 + r / HG, hg = hc * HG + r % HG;
             float v = 0.f;
             if (r < QB * HG && qi < q_len && hg < g)
-                v = to_f32(q[(size_t)(q0 + qi) * q_stride + (size_t)(kvh * g + hg) * hd + d]);
+                v = to_f32(q[(size_t)(q0 + qi) * q_stride + (size_t)(kh * g + hg) * hd + d]);
             q_s[idx] = v;
         }
     }
@@ -159,7 +163,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         if (t0 >= keep && t0 + KT <= blo) { t0 = (blo / KT) * KT - KT; continue; }   // a tile between the kept keys and the window
         __syncthreads();  // previous tile fully consumed
         const int page = table[t0 / RB_PAGE];
-        const size_t base = page >= 0 ? (((size_t)page * nkv + kvh) * RB_PAGE + (t0 % RB_PAGE)) * hd : 0;
+        const size_t base = page >= 0 ? (((size_t)page * n_stored + kh) * RB_PAGE + (t0 % RB_PAGE)) * hd : 0;
+        const size_t base_v = page >= 0 ? (((size_t)page * n_stored + vh) * RB_PAGE + (t0 % RB_PAGE)) * hd : 0;
         if (vec) {
             // A warp takes every fourth key, a lane four consecutive dimensions at a time, and all of a thread's
             // loads are requested before the first is stored: taken one element at a time, each load waited
@@ -171,9 +176,9 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 for (int u = 0; u < KPW; ++u) {
                     const int jj = warp + 4 * u;
                     const bool in = page >= 0 && t0 + jj <= hi && t0 + jj >= lo && (t0 + jj >= blo || t0 + jj < keep);
-                    const size_t off = base + (size_t)jj * hd + d4 * 4;
-                    kk[u] = in ? load4(k_cache + off) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    vv[u] = in ? load4(v_cache + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const size_t off = (size_t)jj * hd + d4 * 4;
+                    kk[u] = in ? load4(k_cache + base + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    vv[u] = in ? load4(v_cache + base_v + off) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
 #pragma unroll
                 for (int u = 0; u < KPW; ++u) {
@@ -188,7 +193,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 const int jj = idx / hd, d = idx - jj * hd;
                 const bool in = page >= 0 && t0 + jj <= hi && t0 + jj >= lo && (t0 + jj >= blo || t0 + jj < keep);
                 k_s[jj * (hd + 1) + d] = in ? to_f32(k_cache[base + idx]) : 0.f;
-                v_s[idx] = in ? to_f32(v_cache[base + idx]) : 0.f;
+                v_s[idx] = in ? to_f32(v_cache[base_v + idx]) : 0.f;
             }
         }
         __syncthreads();
@@ -327,7 +332,7 @@ template <typename T>
 int launch_attn(const void* q, int q_stride, void* out, int o_stride, const void* k_cache, const void* v_cache,
                 const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                 const int* kv_len, int B, int max_q_len, int nq, int nkv, int hd, float scale, int window,
-                int keep, float sink, int chunk, int n_chunks, float* part_acc, float* part_ml, cudaStream_t s) {
+                int keep, float sink, int chunk, int n_chunks, float* part_acc, float* part_ml, int cross, cudaStream_t s) {
     const int g = nq / nkv;
     const int HG = g < ROWS ? g : ROWS;
     const int QB = ROWS / HG;
@@ -343,7 +348,7 @@ int launch_attn(const void* q, int q_stride, void* out, int o_stride, const void
     dim3 grid((unsigned)gx, nkv * head_chunks, B);
     RB_LAUNCH((k), dim3(grid), dim3(128), smem, s, (const T*)q, q_stride, (T*)out, o_stride, (const T*)k_cache, (const T*)v_cache,
                               block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, hd, scale, window,
-                              keep, sink, chunk, n_chunks, part_acc, part_ml);
+                              keep, sink, chunk, n_chunks, part_acc, part_ml, cross);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }
@@ -354,21 +359,22 @@ extern "C" int rb_attention_generic(const void* q, int q_stride, void* out, int 
                                     int max_pages, const int* seq_slot, const int* cu_q, const int* kv_len,
                                     int B, int max_q_len, int nq, int nkv, int hd, float scale, int window,
                                     int keep, float sink, int chunk, int n_chunks, float* part_acc, float* part_ml,
-                                    void* stream) {
+                                    int cross, void* stream) {
     if (B <= 0 || max_q_len <= 0) return RB_OK;
     if (keep < 0 || (keep > 0 && window < 0)) return RB_ERR_BAD_SIZE;
     if (hd <= 0 || hd > 32 * MAX_DPL || nkv <= 0 || nq % nkv) return RB_ERR_BAD_SIZE;
+    if (cross < 0 || (cross > 1 && nkv != cross * cross)) return RB_ERR_BAD_SIZE;
     if (chunk > 0 && (chunk % KT || n_chunks <= 0 || !part_acc || !part_ml)) return RB_ERR_BAD_SIZE;
     if (chunk <= 0) n_chunks = 1;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RB_BF16)
         return launch_attn<__nv_bfloat16>(q, q_stride, out, o_stride, k_cache, v_cache, block_table, max_pages,
                                           seq_slot, cu_q, kv_len, B, max_q_len, nq, nkv, hd, scale, window,
-                                          keep, sink, chunk, n_chunks, part_acc, part_ml, s);
+                                          keep, sink, chunk, n_chunks, part_acc, part_ml, cross, s);
     if (dtype == RB_F32)
         return launch_attn<float>(q, q_stride, out, o_stride, k_cache, v_cache, block_table, max_pages, seq_slot,
                                   cu_q, kv_len, B, max_q_len, nq, nkv, hd, scale, window, keep, sink, chunk, n_chunks,
-                                  part_acc, part_ml, s);
+                                  part_acc, part_ml, cross, s);
     return RB_ERR_BAD_DTYPE;
 }
 

@@ -1,0 +1,310 @@
+// A state-space mixer's recurrence with a step size per token and head, and the short causal convolution before it.
+//
+//   causal_conv   y_t[c] = act(b[c] + sum_j w[c][j] * u_(t - taps + 1 + j)[c])      j = 0 .. taps-1, the last tap is the
+//                 current token's.  u are columns of the layer's stacked projection (in the activations' type, or 32-bit
+//                 partial sums that are added first).  What lies before a sequence's first token of this step comes
+//                 from the sequence's slot ([taps - 1][channels], zeros at the start of a sequence), which then
+//                 receives the step's last taps - 1 inputs.  A block is (sequence, 32 tokens, 128 channels); the block
+//                 of a sequence's first tokens is the only one that reads the slot and rewrites it after its reads.
+//   ssm_scan      per (sequence, head h of group g):  dt = softplus(r_t + bias_h),  a = exp(-exp(A_h) * dt)
+//                 S_t = a S_(t-1) + dt B_t x_t^T          S [n][p], 32-bit, in the slot
+//                 y_t = S_t^T C_t + D_h x_t
+//                 x [heads][p], B and C [groups][n] are columns of the convolution's 32-bit output, r columns of the
+//                 projection.  A block owns a (sequence, head) and a tile of the state's columns, which stays in
+//                 shared memory for the step; eight tokens are staged at a time and every thread walks them over
+//                 its own rows of a column, so no barrier separates tokens.  The order of a token's operations does
+//                 not depend on how the prompt was cut or on the batch.
+//   ssm_scan_blocks   the same for prompts, blocks of 64 tokens side by side.  With c_t = sum_{r <= t} log a_r inside a
+//                 block that starts from S0:
+//                   y_t   = e^(c_t) S0^T C_t + sum_{s <= t} e^(c_t - c_s) (C_t . B_s) dt_s x_s + D x_t
+//                   S_end = e^(c_m) S0 + sum_s e^(c_m - c_s) dt_s B_s x_s^T
+//                 every exponent is <= 0.  Three kernels: each block's own sum; the states the blocks start from, along
+//                 each sequence; each block's outputs.  All 32-bit FMA.
+#include "common.cuh"
+#include "api.h"
+
+using namespace rb;
+
+namespace {
+template <typename IT>
+__device__ __forceinline__ float sum_in(const IT* p, int n_in, size_t in_stride) {
+    float v = 0.f;
+    for (int s = 0; s < n_in; ++s) v += to_f32(p[(size_t)s * in_stride]);
+    return v;
+}
+
+__device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+constexpr int CONV_TOK = 32;
+constexpr int CONV_CH = 128;
+constexpr int CONV_MAX_TAPS = 16;
+
+template <typename IT>
+__global__ void __launch_bounds__(CONV_CH)
+causal_conv_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int col0, int channels, int taps,
+                   const float* __restrict__ w, const float* __restrict__ bias, int act, float* __restrict__ kept,
+                   const int* __restrict__ seq_slot, const int* __restrict__ cu_q, float* __restrict__ out, int ld_out) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.z;
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    const int t_begin = cu_q[b], t_end = cu_q[b + 1];
+    const int t0 = t_begin + blockIdx.y * CONV_TOK;
+    if (t0 >= t_end) return;
+    const int c = blockIdx.x * CONV_CH + threadIdx.x;
+    const bool live = c < channels;
+    const int back = taps - 1;
+    float* mine = kept + (size_t)slot * back * channels;          // [taps - 1][channels]
+    float wt[CONV_MAX_TAPS], win[CONV_MAX_TAPS];                  // the taps, and the last inputs (win[taps-1]: the newest)
+    float bc = 0.f;
+    if (live) {
+        bc = bias ? bias[c] : 0.f;
+        for (int j = 0; j < taps; ++j) wt[j] = w[(size_t)c * taps + j];
+        for (int j = 0; j < back; ++j) {
+            const int t = t0 - back + j;                          // the row `back - j` before the block's first
+            win[j + 1] = t >= t_begin ? sum_in(in + (size_t)t * row_stride + col0 + c, n_in, in_stride)
+                                      : mine[(size_t)(back + (t - t_begin)) * channels + c];
+        }
+    }
+    const int n = min(CONV_TOK, t_end - t0);
+    if (live) {
+        for (int tt = 0; tt < n; ++tt) {
+            for (int j = 0; j < back; ++j) win[j] = win[j + 1];
+            win[back] = sum_in(in + (size_t)(t0 + tt) * row_stride + col0 + c, n_in, in_stride);
+            float acc = bc;
+            for (int j = 0; j < taps; ++j) acc = fmaf(wt[j], win[j], acc);
+            if (act == 1) acc = silu(acc);
+            out[(size_t)(t0 + tt) * ld_out + c] = acc;
+        }
+    }
+    // Only the block of a sequence's first tokens reads the slot (a block spans more tokens than there are taps), and
+    // a channel's rows are read and written by one thread alone: that thread leaves the step's last inputs there.
+    if (blockIdx.y == 0 && live) {
+        // new rows of the slot: the last `back` inputs of (old rows, this step's rows)
+        const int len = t_end - t_begin;
+        float fresh[CONV_MAX_TAPS];
+        for (int j = 0; j < back; ++j) {
+            const int src = len + j;                               // index into the concatenation of old and new rows
+            fresh[j] = src < back ? mine[(size_t)src * channels + c]
+                                  : sum_in(in + (size_t)(t_begin + src - back) * row_stride + col0 + c, n_in, in_stride);
+        }
+        for (int j = 0; j < back; ++j) mine[(size_t)j * channels + c] = fresh[j];
+    }
+}
+
+constexpr int SCAN_THREADS = 256;
+constexpr int SCAN_TB = 8;
+
+template <typename IT>
+__global__ void __launch_bounds__(SCAN_THREADS)
+ssm_scan_kernel(const float* __restrict__ u, int ld_u, int x_off, int b_off, int c_off, const IT* __restrict__ raw, int n_in,
+                size_t in_stride, int row_stride, int dt_off, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                const float* __restrict__ skip, int heads, int groups, int n, int p, float* __restrict__ state,
+                const int* __restrict__ seq_slot, const int* __restrict__ cu_q, float* __restrict__ out, int ld_out, int VT, int P) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    float* S = sm;                              // [n][VT]
+    float* cs = S + (size_t)n * VT;             // [TB][n]   C_t
+    float* bs = cs + SCAN_TB * n;               // [TB][n]   dt_t * B_t
+    float* xs = bs + SCAN_TB * n;               // [TB][VT]
+    float* part = xs + SCAN_TB * VT;            // [TB][P][VT]
+    float* dec = part + SCAN_TB * P * VT;       // [TB] decays, [TB] step sizes
+    const int b = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * VT;
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    const int t_begin = cu_q[b], t_end = cu_q[b + 1];
+    if (t_end <= t_begin) return;
+    const int g = h / (heads / groups);
+    const int vt = min(VT, p - v0);
+    const int tid = threadIdx.x;
+    const float rate = expf(a_log[h]), db = dt_bias[h], dskip = skip[h];
+    float* st = state + (((size_t)slot * heads + h) * n) * p + v0;
+    for (int idx = tid; idx < n * VT; idx += SCAN_THREADS) {
+        const int i = idx / VT, j = idx - i * VT;
+        S[idx] = j < vt ? st[(size_t)i * p + j] : 0.f;
+    }
+    const int pp = tid / VT, j = tid - pp * VT;
+    const bool works = pp < P && j < vt;
+    for (int t0 = t_begin; t0 < t_end; t0 += SCAN_TB) {
+        const int nb = min(SCAN_TB, t_end - t0);
+        __syncthreads();                        // the tokens before are done with the staging buffers
+        if (tid < nb) {
+            const float dt = softplus_f32(sum_in(raw + (size_t)(t0 + tid) * row_stride + dt_off + h, n_in, in_stride) + db);
+            dec[tid] = expf(-rate * dt);
+            dec[SCAN_TB + tid] = dt;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nb * n; idx += SCAN_THREADS) {
+            const int tt = idx / n, i = idx - tt * n;
+            const float* row = u + (size_t)(t0 + tt) * ld_u + (size_t)g * n + i;
+            cs[idx] = row[c_off];
+            bs[idx] = row[b_off] * dec[SCAN_TB + tt];
+        }
+        for (int idx = tid; idx < nb * VT; idx += SCAN_THREADS) {
+            const int tt = idx / VT, jj = idx - tt * VT;
+            xs[idx] = jj < vt ? u[(size_t)(t0 + tt) * ld_u + x_off + (size_t)h * p + v0 + jj] : 0.f;
+        }
+        __syncthreads();
+        if (works) {
+            for (int tt = 0; tt < nb; ++tt) {
+                const float x = xs[tt * VT + j], a = dec[tt];
+                const float* cc = cs + tt * n;
+                const float* bb = bs + tt * n;
+                float acc = 0.f;
+                for (int i = pp; i < n; i += P) {
+                    const float s = fmaf(bb[i], x, a * S[i * VT + j]);
+                    S[i * VT + j] = s;
+                    acc = fmaf(s, cc[i], acc);
+                }
+                part[(tt * P + pp) * VT + j] = acc;
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nb * VT; idx += SCAN_THREADS) {
+            const int tt = idx / VT, jj = idx - tt * VT;
+            if (jj >= vt) continue;
+            float o = 0.f;
+            for (int q = 0; q < P; ++q) o += part[(tt * P + q) * VT + jj];
+            out[(size_t)(t0 + tt) * ld_out + (size_t)h * p + v0 + jj] = fmaf(dskip, xs[idx], o);
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < n * VT; idx += SCAN_THREADS) {
+        const int i = idx / VT, jj = idx - i * VT;
+        if (jj < vt) st[(size_t)i * p + jj] = S[idx];
+    }
+}
+// What follows the recurrence: y times act(z), z columns of the projection (the gate comes first), then divided by
+// the root mean square of each of `groups` equal parts of the row (eps inside the root), times a weight vector;
+// written in the activations' type for the output product.  One block a token, the gated row in shared memory; few
+// groups are summed by the whole block one after another, many by a warp each.
+template <typename IT, typename AT>
+__global__ void __launch_bounds__(256)
+gate_group_norm_kernel(const float* __restrict__ y, int ld_y, const IT* __restrict__ proj, int n_in, size_t in_stride,
+                       int row_stride, int z_off, const float* __restrict__ w, float eps, int groups, int W, int gate_act,
+                       AT* __restrict__ out, int ld_out, const int* __restrict__ slot_of_token) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float rowbuf[];       // W floats + 33
+    float* red = rowbuf + W;
+    const int t = blockIdx.x;
+    if (slot_of_token[t] < 0) return;
+    const float* src = y + (size_t)t * ld_y;
+    const IT* z = proj + (size_t)t * row_stride + z_off;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float g = sum_in(z + i, n_in, in_stride);
+        rowbuf[i] = src[i] * (gate_act == 1 ? silu(g) : (gate_act == 2 ? sigmoid_f32(g) : 1.f));
+    }
+    __syncthreads();
+    const int gw = W / groups;
+    AT* dst = out + (size_t)t * ld_out;
+    if (groups <= 8) {
+        for (int gi = 0; gi < groups; ++gi) {
+            float ss = 0.f;
+            for (int i = threadIdx.x; i < gw; i += blockDim.x) { const float v = rowbuf[gi * gw + i]; ss = fmaf(v, v, ss); }
+            const float inv = rsqrtf(block_sum(ss, red) / (float)gw + eps);
+            for (int i = threadIdx.x; i < gw; i += blockDim.x) {
+                const int c = gi * gw + i;
+                dst[c] = from_f32<AT>(rowbuf[c] * inv * (w ? w[c] : 1.f));
+            }
+        }
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int gi = warp; gi < groups; gi += nwarps) {
+        float ss = 0.f;
+        for (int i = lane; i < gw; i += 32) { const float v = rowbuf[gi * gw + i]; ss = fmaf(v, v, ss); }
+        const float inv = rsqrtf(warp_sum(ss) / (float)gw + eps);
+        for (int i = lane; i < gw; i += 32) {
+            const int c = gi * gw + i;
+            dst[c] = from_f32<AT>(rowbuf[c] * inv * (w ? w[c] : 1.f));
+        }
+    }
+}
+}  // namespace
+
+extern "C" int rb_gate_group_norm(const float* y, int ld_y, const void* proj, int proj_dtype, int n_in, long long in_stride,
+                                  int row_stride, int z_off, const float* w, float eps, int groups, int W, int gate_act,
+                                  void* out, int out_dtype, int ld_out, const int* slot_of_token, int T, void* stream) {
+    if (T <= 0) return RB_OK;
+    if (groups <= 0 || W <= 0 || W % groups || n_in < 1) return RB_ERR_BAD_SIZE;
+    const size_t smem = (size_t)(W + 33) * sizeof(float);
+    if (smem > 200 * 1024) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+#define RB_GGN(IT, AT)                                                                                                    \
+    do {                                                                                                                  \
+        auto k = gate_group_norm_kernel<IT, AT>;                                                                          \
+        if (smem > 48 * 1024) {                                                                                           \
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
+            if (e != cudaSuccess) return (int)e;                                                                          \
+        }                                                                                                                 \
+        RB_LAUNCH((k), dim3(T), dim3(256), smem, s, y, ld_y, (const IT*)proj, n_in, (size_t)in_stride, row_stride, z_off, w, \
+                  eps, groups, W, gate_act, (AT*)out, ld_out, slot_of_token);                                              \
+    } while (0)
+    if (proj_dtype == RB_BF16 && out_dtype == RB_BF16) RB_GGN(bf, bf);
+    else if (proj_dtype == RB_F32 && out_dtype == RB_BF16) RB_GGN(float, bf);
+    else if (proj_dtype == RB_F32 && out_dtype == RB_F32) RB_GGN(float, float);
+    else return RB_ERR_BAD_DTYPE;
+#undef RB_GGN
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+extern "C" int rb_causal_conv(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int col0,
+                              int channels, int taps, const float* w, const float* bias, int act, float* kept,
+                              const int* seq_slot, const int* cu_q, int n_seqs, int max_q_len, float* out, int ld_out,
+                              void* stream) {
+    if (n_seqs <= 0 || max_q_len <= 0) return RB_OK;
+    if (channels <= 0 || taps < 1 || taps > CONV_MAX_TAPS || n_in < 1 || n_seqs > 65535) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((channels + CONV_CH - 1) / CONV_CH, (max_q_len + CONV_TOK - 1) / CONV_TOK, n_seqs);
+    if (grid.y > 65535) return RB_ERR_BAD_SIZE;
+    if (in_dtype == RB_F32)
+        RB_LAUNCH((causal_conv_kernel<float>), grid, dim3(CONV_CH), 0, s, (const float*)in, n_in, (size_t)in_stride, row_stride,
+                  col0, channels, taps, w, bias, act, kept, seq_slot, cu_q, out, ld_out);
+    else if (in_dtype == RB_BF16)
+        RB_LAUNCH((causal_conv_kernel<__nv_bfloat16>), grid, dim3(CONV_CH), 0, s, (const __nv_bfloat16*)in, n_in,
+                  (size_t)in_stride, row_stride, col0, channels, taps, w, bias, act, kept, seq_slot, cu_q, out, ld_out);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+extern "C" int rb_ssm_scan(const float* u, int ld_u, int x_off, int b_off, int c_off, const void* raw, int raw_dtype, int n_in,
+                           long long in_stride, int row_stride, int dt_off, const float* dt_bias, const float* a_log,
+                           const float* skip, int heads, int groups, int n, int p, float* state, const int* seq_slot,
+                           const int* cu_q, int n_seqs, float* out, int ld_out, void* stream) {
+    if (n_seqs <= 0) return RB_OK;
+    if (heads <= 0 || groups <= 0 || heads % groups || n <= 0 || p <= 0 || n_in < 1 || n_seqs > 65535 || heads > 65535)
+        return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    // a tile of the state's columns: as wide as 64 KB of shared memory hold with n rows, at most 64, at most p
+    int VT = p < 64 ? p : 64;
+    while (VT > 1 && (size_t)n * VT * sizeof(float) > 64 * 1024) VT = (VT + 1) / 2;
+    int P = SCAN_THREADS / VT;
+    if (P > n) P = n;
+    if (P < 1) P = 1;
+    const size_t smem = ((size_t)n * VT + 2 * SCAN_TB * n + SCAN_TB * VT + (size_t)SCAN_TB * P * VT + 2 * SCAN_TB) * sizeof(float);
+    if (smem > 200 * 1024) return RB_ERR_BAD_SIZE;
+    const dim3 grid((p + VT - 1) / VT, heads, n_seqs);
+#define RB_SCAN(IT)                                                                                                          \
+    do {                                                                                                                     \
+        auto k = ssm_scan_kernel<IT>;                                                                                        \
+        if (smem > 48 * 1024) {                                                                                              \
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                 \
+            if (e != cudaSuccess) return (int)e;                                                                             \
+        }                                                                                                                    \
+        RB_LAUNCH((k), grid, dim3(SCAN_THREADS), smem, s, u, ld_u, x_off, b_off, c_off, (const IT*)raw, n_in, (size_t)in_stride, \
+                  row_stride, dt_off, dt_bias, a_log, skip, heads, groups, n, p, state, seq_slot, cu_q, out, ld_out, VT, P);  \
+    } while (0)
+    if (raw_dtype == RB_F32) RB_SCAN(float);
+    else if (raw_dtype == RB_BF16) RB_SCAN(__nv_bfloat16);
+    else return RB_ERR_BAD_DTYPE;
+#undef RB_SCAN
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}

@@ -1,0 +1,164 @@
+// Attention whose heads' weights are mixed after the softmax, and whose queries and keys are normalised over the
+// whole projection.
+//
+// With a'_h = sum_g M[h][g] a_g and head h reading the values of its own key/value head m(h), the result is
+// o_h = sum_g M[h][g] (sum_j a_g(i, j) v_m(h)(j)): every query head's weights applied to the values of every stored
+// head (the attention kernels' `cross` mode, result (g, m) for each pair), then a small product over g.
+//
+//   wide_norm_rope_cache   a token's projection row [q (nq * hd) | k (nkv * hd) | v (nkv * vd)] (in the activations' type,
+//                 or 32-bit partial sums added first): q and k are each divided by their root mean square over ALL
+//                 their heads together and multiplied by a weight vector of that width; the first rot entries of every
+//                 head turn by the step's table (neighbouring pairs, or pairs half a rotation apart); query head h is
+//                 multiplied by factor[h] (a temperature on its scores); q goes out padded to hdp a head, k and v into
+//                 the token's place in the paged cache, padded alike.  32-bit until the stores.  One block a token.
+//   talk_mix      out[t][h][:] = sum_g M[h][g] * o[t][pair (g, m(h))][:], 32-bit sums, padding dropped.
+#include "common.cuh"
+#include "api.h"
+
+using namespace rb;
+
+namespace {
+template <typename IT>
+__device__ __forceinline__ float sum_parts(const IT* p, size_t stride, int n_in) {
+    float v = 0.f;
+    for (int s = 0; s < n_in; ++s) v += to_f32(p[(size_t)s * stride]);
+    return v;
+}
+
+// entry d of a head whose entries x[0 .. rot) turn: cs = (cos, sin) pairs of the token, half = rot / 2
+__device__ __forceinline__ float turned(const float* x, int d, int rot, bool neighbours, const float* cs) {
+    if (d >= rot) return x[d];
+    const int half = rot >> 1;
+    if (neighbours) {
+        const int i = d >> 1;
+        const float c = cs[2 * i], s = cs[2 * i + 1];
+        return (d & 1) ? x[d] * c + x[d - 1] * s : x[d] * c - x[d + 1] * s;
+    }
+    const int i = d < half ? d : d - half;
+    const float c = cs[2 * i], s = cs[2 * i + 1];
+    return d < half ? x[d] * c - x[d + half] * s : x[d] * c + x[d - half] * s;
+}
+
+template <typename IT, typename AT>
+__global__ void __launch_bounds__(256)
+wide_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int nq, int nkv, int hd,
+                            int vd, int hdp, const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                            const float* __restrict__ factor, const float* __restrict__ cos_sin, int rot, int neighbours,
+                            AT* __restrict__ q_out, int q_stride, AT* __restrict__ k_cache, AT* __restrict__ v_cache,
+                            const int* __restrict__ positions, const int* __restrict__ slot_of_token,
+                            const int* __restrict__ block_table, int max_pages) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float buf[];            // (nq + nkv) * hd floats + 33
+    const int qw = nq * hd, kw = nkv * hd;
+    float* kb = buf + qw;
+    float* red = kb + kw;
+    const int t = blockIdx.x;
+    const int slot = slot_of_token[t];
+    if (slot < 0) return;
+    const IT* row = in + (size_t)t * row_stride;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < qw + kw; i += blockDim.x) {
+        const float v = sum_parts(row + i, in_stride, n_in);
+        buf[i] = v;
+        if (i < qw) sq += v * v; else sk += v * v;
+    }
+    const float inv_q = wq ? rsqrtf(block_sum(sq, red) / (float)qw + eps) : 1.f;
+    const float inv_k = wk ? rsqrtf(block_sum(sk, red) / (float)kw + eps) : 1.f;
+    for (int i = threadIdx.x; i < qw + kw; i += blockDim.x) {
+        if (i < qw) { if (wq) buf[i] *= inv_q * wq[i]; }
+        else if (wk) buf[i] *= inv_k * wk[i - qw];
+    }
+    __syncthreads();
+    const float* cs = cos_sin ? cos_sin + (size_t)t * (rot >> 1) * 2 : nullptr;
+    const int r = cs ? rot : 0;
+    for (int i = threadIdx.x; i < nq * hdp; i += blockDim.x) {
+        const int h = i / hdp, d = i - h * hdp;
+        float v = 0.f;
+        if (d < hd) v = turned(buf + h * hd, d, r, neighbours != 0, cs) * (factor ? factor[h] : 1.f);
+        q_out[(size_t)t * q_stride + i] = from_f32<AT>(v);
+    }
+    const int pos = positions[t];
+    const int page = block_table[(size_t)slot * max_pages + pos / RB_PAGE];
+    if (page < 0) return;
+    for (int i = threadIdx.x; i < nkv * hdp; i += blockDim.x) {
+        const int h = i / hdp, d = i - h * hdp;
+        const size_t at = (((size_t)page * nkv + h) * RB_PAGE + (pos % RB_PAGE)) * hdp + d;
+        k_cache[at] = from_f32<AT>(d < hd ? turned(kb + h * hd, d, r, neighbours != 0, cs) : 0.f);
+        v_cache[at] = from_f32<AT>(d < vd ? sum_parts(row + qw + kw + h * vd + d, in_stride, n_in) : 0.f);
+    }
+}
+
+template <typename AT>
+__global__ void talk_mix_kernel(const AT* __restrict__ o, int o_stride, const float* __restrict__ mix, AT* __restrict__ out,
+                                int out_stride, int nq, int nkv, int hdp, int vd, const int* __restrict__ slot_of_token, int T) {
+    pdl_trigger();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)T * nq * vd) return;
+    const int d = (int)(idx % vd);
+    const int h = (int)((idx / vd) % nq);
+    const int t = (int)(idx / ((long long)vd * nq));
+    if (slot_of_token[t] < 0) return;
+    const int gs = nq / nkv, m = h / gs;
+    const AT* row = o + (size_t)t * o_stride + d;
+    float acc = 0.f;
+    for (int g = 0; g < nq; ++g) {
+        const int a = g / gs;
+        const int pair = (a * nkv + m) * gs + (g - a * gs);
+        acc = fmaf(mix[h * nq + g], to_f32(row[(size_t)pair * hdp]), acc);
+    }
+    out[(size_t)t * out_stride + (size_t)h * vd + d] = from_f32<AT>(acc);
+}
+}  // namespace
+
+extern "C" int rb_wide_norm_rope_cache(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int nq,
+                                       int nkv, int hd, int vd, int hdp, const float* wq, const float* wk, float eps,
+                                       const float* factor, const float* cos_sin, int rot, int neighbours, void* q_out,
+                                       int q_stride, void* k_cache, void* v_cache, int act_dtype, const int* positions,
+                                       const int* slot_of_token, const int* block_table, int max_pages, int T, void* stream) {
+    if (T <= 0) return RB_OK;
+    if (nq <= 0 || nkv <= 0 || hd <= 0 || vd <= 0 || hdp < hd || hdp < vd || rot < 0 || (rot & 1) || rot > hd || n_in < 1)
+        return RB_ERR_BAD_SIZE;
+    const size_t smem = (size_t)((nq + nkv) * hd + 33) * sizeof(float);
+    if (smem > 200 * 1024) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+#define RB_WN(IT, AT)                                                                                                    \
+    do {                                                                                                                 \
+        auto k = wide_norm_rope_cache_kernel<IT, AT>;                                                                    \
+        if (smem > 48 * 1024) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
+            if (e != cudaSuccess) return (int)e;                                                                         \
+        }                                                                                                                \
+        RB_LAUNCH((k), dim3(T), dim3(256), smem, s, (const IT*)in, n_in, (size_t)in_stride, row_stride, nq, nkv, hd, vd, \
+                  hdp, wq, wk, eps, factor, cos_sin, rot, neighbours, (AT*)q_out, q_stride, (AT*)k_cache, (AT*)v_cache,  \
+                  positions, slot_of_token, block_table, max_pages);                                                     \
+    } while (0)
+    if (in_dtype == RB_F32 && act_dtype == RB_BF16) RB_WN(float, bf);
+    else if (in_dtype == RB_BF16 && act_dtype == RB_BF16) RB_WN(bf, bf);
+    else if (in_dtype == RB_F32 && act_dtype == RB_F32) RB_WN(float, float);
+    else return RB_ERR_BAD_DTYPE;
+#undef RB_WN
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+extern "C" int rb_talk_mix(const void* o, int o_stride, const float* mix, void* out, int out_stride, int nq, int nkv, int hdp,
+                           int vd, int dtype, const int* slot_of_token, int T, void* stream) {
+    if (T <= 0) return RB_OK;
+    if (nq <= 0 || nkv <= 0 || nq % nkv || vd <= 0 || hdp < vd) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long blocks = ((long long)T * nq * vd + 255) / 256;
+    if (blocks > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
+    if (dtype == RB_BF16)
+        RB_LAUNCH((talk_mix_kernel<__nv_bfloat16>), dim3((unsigned)blocks), dim3(256), 0, s, (const __nv_bfloat16*)o, o_stride, mix,
+                  (__nv_bfloat16*)out, out_stride, nq, nkv, hdp, vd, slot_of_token, T);
+    else if (dtype == RB_F32)
+        RB_LAUNCH((talk_mix_kernel<float>), dim3((unsigned)blocks), dim3(256), 0, s, (const float*)o, o_stride, mix, (float*)out,
+                  out_stride, nq, nkv, hdp, vd, slot_of_token, T);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}

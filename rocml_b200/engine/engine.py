@@ -97,9 +97,9 @@ class Engine:
             return
         esz = 4 if self.env.act_dtype == torch.float32 else 2
         per_token = state = 0
-        for r, src in zip(self.model.cache_requirements(), self.model.reads_cache_of()):
-            if src is not None or r is None:
-                continue
+        from ..cache.requirements import simple_requirements
+        for r in [x for r, src in zip(self.model.cache_requirements(), self.model.reads_cache_of()) if src is None
+                  for x in simple_requirements(r)]:
             if hasattr(r, "n_kv_heads"):
                 per_token += (1 if getattr(r, "shared_values", False) else 2) * r.n_kv_heads * r.head_dim * esz
             elif hasattr(r, "shape"):

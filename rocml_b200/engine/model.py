@@ -131,7 +131,9 @@ class Model:
             (self.embedding_norm is None or self.embedding_norm.graph_safe)
 
     def cache_requirements(self):
-        return [self.blocks[e.layer].mixer.cache_requirement() for e in self.spec.schedule]
+        # an arrangement that keeps something of its own a sequence (the row of the token before) answers for its layer
+        return [getattr(self.blocks[e.layer], "cache_requirement", self.blocks[e.layer].mixer.cache_requirement)()
+                for e in self.spec.schedule]
 
     def reads_cache_of(self):
         return [e.reads_cache_of for e in self.spec.schedule]

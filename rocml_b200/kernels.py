@@ -135,7 +135,7 @@ def _lib():
         lib.rb_rope_table.argtypes = [_vp, _vp, _i, _i, _f, _vp, _vp]
         lib.rb_gemm_generic.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _vp]
         lib.rb_attention_generic.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i,
-                                             _i, _i, _i, _f, _i, _i, _f, _i, _i, _vp, _vp, _vp]
+                                             _i, _i, _i, _f, _i, _i, _f, _i, _i, _vp, _vp, _i, _vp]
         lib.rb_attention_merge.argtypes = [_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp]
         lib.rb_argmax.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _i, _vp]
         lib.rb_attention_prefill.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
@@ -180,6 +180,18 @@ def _lib():
                                              _i, _vp, _vp, _i, _vp]
         lib.rb_group_norm_gate.argtypes = [_vp, _i, _vp, _i, _i, _ll, _i, _i, _vp, _i, _f, _i, _i, _i, _vp, _i, _i, _vp,
                                            _i, _vp]
+        lib.rb_postln.argtypes = [_vp, _vp, _i, _ll, _vp, _vp, _f, _f, _vp, _i, _vp, _i, _i, _vp]
+        lib.rb_token_shift.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp]
+        lib.rb_causal_conv.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]
+        lib.rb_ssm_scan.argtypes = [_vp, _i, _i, _i, _i, _vp, _i, _i, _ll, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp,
+                                    _vp, _i, _vp, _i, _vp]
+        lib.rb_gate_group_norm.argtypes = [_vp, _i, _vp, _i, _i, _ll, _i, _i, _vp, _f, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp]
+        lib.rb_latent_rot_prep.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _vp,
+                                           _vp, _vp, _vp, _i, _i, _vp]
+        lib.rb_latent_q_rot.argtypes = [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _vp, _i, _vp]
+        lib.rb_wide_norm_rope_cache.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _i, _i, _vp,
+                                                _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp]
+        lib.rb_talk_mix.argtypes = [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp]
         lib.rb_gemm_tcgen05_set_wait.argtypes = [_ll, _i]
         lib.rb_gemm_tcgen05_set_wait.restype = None
         _sigs_done = True
@@ -403,19 +415,23 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                       n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
                       chunk: int = 0, n_chunks: int = 1, part_acc: Optional[torch.Tensor] = None,
-                      part_ml: Optional[torch.Tensor] = None, keep: int = 0, sink: Optional[float] = None):
+                      part_ml: Optional[torch.Tensor] = None, keep: int = 0, sink: Optional[float] = None, cross: int = 0):
     """q rows [T, >= nq*hd] (row stride free) -> out rows [T, >= nq*hd]; keys and values from the pages.
     ``keep``: the keys at positions below it stay visible beside the window; ``sink``: a score that adds
-    exp(sink) to every row's denominator and brings no value (None: no such term)."""
+    exp(sink) to every row's denominator and brings no value (None: no such term).  ``cross`` (n > 1, the cache's
+    own number of key/value heads): every query head's weights are applied to the values of EVERY stored head;
+    ``nkv`` = n * n then counts (key head, value head) pairs, ``nq`` = n * query heads the results, pair
+    (a, m) at a * n + m with the results of key head a's queries in their order, and q holds nq / n heads."""
     if q.stride(-1) != 1 or out.stride(-1) != 1 or q.dtype != out.dtype or k_cache.dtype != q.dtype:
         raise KernelError("attention_generic: strides or types do not fit")
-    if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
+    stored = nkv // cross if cross > 1 else nkv
+    if tuple(k_cache.shape[1:]) != (stored, PAGE, hd) or k_cache.shape != v_cache.shape:
         raise KernelError("attention_generic: cache must be [pages, nkv, 64, hd]")
     rc = _lib().rb_attention_generic(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), dtype_code(q.dtype), _ptr(k_cache), _ptr(v_cache),
         _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"),
         _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window), int(keep), _sink(sink),
-        int(chunk), int(n_chunks), _ptr(part_acc), _ptr(part_ml), _stream())
+        int(chunk), int(n_chunks), _ptr(part_acc), _ptr(part_ml), int(cross), _stream())
     _check(rc, "attention_generic")
 
 
@@ -1303,16 +1319,22 @@ def head_gate(x: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], 
 @_profiled(lambda a, facts: (a["w"].numel() * _esz(a["w"]) + a["m"] * a["w"].shape[0] * (a["w"].shape[2] * _esz(a["x"])
                                                                                            + a["w"].shape[1] * _esz(a["out"])),
                              2 * a["m"] * a["w"].shape[0] * a["w"].shape[1] * a["w"].shape[2]))
-def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, m: int, row_scale: Optional[torch.Tensor] = None):
+def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, m: int, row_scale: Optional[torch.Tensor] = None,
+                x_group_stride: Optional[int] = None, out_group_stride: Optional[int] = None):
     """Per-head products: out[t, g * N : (g + 1) * N] = x[t, g * K : (g + 1) * K] . w[g]^T for w [G, N, K]; rows may be
-    strided.  ``row_scale`` float32 [T, G] multiplies head g's result for row t."""
+    strided.  ``row_scale`` float32 [T, G] multiplies head g's result for row t.  ``x_group_stride`` / ``out_group_stride``:
+    head g reads from column g * x_group_stride and writes from column g * out_group_stride instead (heads that sit
+    in wider rows: only part of each head is read, or the results leave room behind them)."""
     G, N, K = w.shape
-    if x.stride(-1) != 1 or out.stride(-1) != 1 or x.shape[-1] < G * K or out.shape[-1] < G * N or not w.is_contiguous():
+    xs = K if x_group_stride is None else int(x_group_stride)
+    os_ = N if out_group_stride is None else int(out_group_stride)
+    if x.stride(-1) != 1 or out.stride(-1) != 1 or xs < K or os_ < N or x.shape[-1] < (G - 1) * xs + K or \
+            out.shape[-1] < (G - 1) * os_ + N or not w.is_contiguous():
         raise KernelError("head_matmul: shapes or strides do not fit")
     if row_scale is not None and (row_scale.dtype != torch.float32 or not row_scale.is_contiguous() or row_scale.shape[-1] != G):
         raise KernelError("head_matmul: row_scale must be contiguous float32 [T, G]")
-    rc = _lib().rb_grouped_matmul(_ptr(x), dtype_code(x.dtype), x.stride(0), K, _ptr(w), dtype_code(w.dtype), N * K,
-                                  _ptr(out), dtype_code(out.dtype), out.stride(0), N, m, N, K, G, None, 0,
+    rc = _lib().rb_grouped_matmul(_ptr(x), dtype_code(x.dtype), x.stride(0), xs, _ptr(w), dtype_code(w.dtype), N * K,
+                                  _ptr(out), dtype_code(out.dtype), out.stride(0), os_, m, N, K, G, None, 0,
                                   _ptr(row_scale), G, 0, 0.0, 1.0, _stream())
     _check(rc, "head_matmul")
 
@@ -1379,3 +1401,212 @@ def tile_matmul_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_gr
         return False
     _check(rc, "tile_matmul_tc5")
     return True
+
+
+# ---- a layer whose norm follows the sum; the blend with the token before ---------------------------------------------
+
+def _f32vec(t: Optional[torch.Tensor], n: int, what: str):
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n:
+        raise KernelError(f"{what} must be contiguous float32 with {n} numbers")
+    return _ptr(t)
+
+
+@_profiled(lambda a, facts: (a["resid"].shape[1] * ((a["n_rows"] or a["resid"].shape[0]) * (8 + 4 * _n_partials(a["delta"])
+                             + (_esz(a["out"]) if a["out"] is not None else 0)) + 8), 6 * (a["n_rows"] or a["resid"].shape[0]) * a["resid"].shape[1]))
+def postln(resid: torch.Tensor, delta: Optional[torch.Tensor], gain: Optional[torch.Tensor], weight: torch.Tensor, alpha: float,
+           eps: float, out: Optional[torch.Tensor], slot_of_token: Optional[torch.Tensor] = None, n_rows: Optional[int] = None):
+    """resid [T, H] float32 <- rmsnorm(alpha * resid + gain * sum_s delta[s]) * weight, in place; ``delta`` float32
+    [S, >= T, H] partial sums (or None), ``gain`` and ``weight`` float32 [H]; ``out`` [T, H] also receives the rows in its
+    own type.  Rows whose slot is -1 are left alone."""
+    T, H = resid.shape
+    n = T if n_rows is None else n_rows
+    if resid.dtype != torch.float32 or not resid.is_contiguous():
+        raise KernelError("postln: resid must be contiguous float32")
+    n_delta, stride = 0, 0
+    if delta is not None:
+        if delta.dtype != torch.float32 or not delta.is_contiguous() or delta.dim() != 3 or delta.shape[1] < n or delta.shape[2] != H:
+            raise KernelError("postln: delta must be contiguous float32 [S, >= T, H]")
+        n_delta, stride = delta.shape[0], delta.stride(0)
+    if out is not None and (not out.is_contiguous() or out.shape[-1] != H or out.numel() < n * H):
+        raise KernelError("postln: out must be contiguous [T, H]")
+    rc = _lib().rb_postln(_ptr(resid), _ptr(delta), n_delta, stride, _f32vec(gain, H, "postln: gain"),
+                          _f32vec(weight, H, "postln: weight"), float(alpha), float(eps), _ptr(out),
+                          dtype_code(out.dtype) if out is not None else F32,
+                          None if slot_of_token is None else _i32(slot_of_token, "slot_of_token"), n, H, _stream())
+    _check(rc, "postln")
+
+
+@_profiled(lambda a, facts: (a["x"].shape[1] * (a["n_tokens"] * (4 + _esz(a["out"])) + 4 + 8 * a["n_seqs"]), 2 * a["n_tokens"] * a["x"].shape[1]))
+def token_shift(x: torch.Tensor, mu: torch.Tensor, kept: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, n_seqs: int,
+                max_q_len: int, out: torch.Tensor, n_tokens: int):
+    """out[t] = x[t] + (x[t - 1] - x[t]) * mu over each sequence's rows of the step; the row before a sequence's first is
+    ``kept[slot]`` (float32 [slots, H]), which then receives the sequence's last row.  x float32 [T, H]."""
+    H = x.shape[1]
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or out.shape[-1] != H or out.shape[0] < n_tokens:
+        raise KernelError("token_shift: x must be contiguous float32 [T, H], out contiguous [T, H]")
+    if kept.dtype != torch.float32 or not kept.is_contiguous() or kept.shape[-1] != H:
+        raise KernelError("token_shift: kept must be contiguous float32 [slots, H]")
+    rc = _lib().rb_token_shift(_ptr(x), _f32vec(mu, H, "token_shift: mu"), _ptr(kept), _i32(seq_slot, "seq_slot"),
+                               _i32(cu_q, "cu_q"), n_seqs, max_q_len, _ptr(out), dtype_code(out.dtype), H, _stream())
+    _check(rc, "token_shift")
+
+
+# ---- a state-space mixer ------------------------------------------------------------------------------------------------
+
+CONV_MAX_TAPS = 16
+
+
+@_profiled(lambda a, facts: (a["n_tokens"] * a["channels"] * (4 + _esz(a["proj"]) * _n_in(a["proj"])) + a["channels"] * 4 * (a["taps"] + 1),
+                             2 * a["n_tokens"] * a["channels"] * a["taps"]))
+def causal_conv(proj: torch.Tensor, n_tokens: int, col0: int, channels: int, taps: int, weight: torch.Tensor,
+                bias: Optional[torch.Tensor], act: str, kept: Optional[torch.Tensor], seq_slot: torch.Tensor, cu_q: torch.Tensor,
+                n_seqs: int, max_q_len: int, out: torch.Tensor):
+    """out float32 [T, channels] = act(bias + causal convolution with ``taps`` taps) of columns col0 .. col0 + channels of
+    ``proj`` ([T, N] or [S, T, N] float32 partial sums).  ``weight`` float32 [channels, taps] (the last tap is the current
+    token's); ``kept`` float32 [slots, taps - 1, channels]: the inputs before each sequence's first token of the step, read
+    and then replaced by the step's last ones."""
+    n_in, in_stride, row_stride = _partials(proj, "causal_conv")
+    if taps < 1 or taps > CONV_MAX_TAPS or col0 + channels > proj.shape[-1]:
+        raise KernelError(f"causal_conv: 1 to {CONV_MAX_TAPS} taps, and the channels inside the projection rows")
+    if weight.dtype != torch.float32 or not weight.is_contiguous() or tuple(weight.shape) != (channels, taps):
+        raise KernelError("causal_conv: weight must be contiguous float32 [channels, taps]")
+    if taps > 1 and (kept is None or kept.dtype != torch.float32 or not kept.is_contiguous() or tuple(kept.shape[1:]) != (taps - 1, channels)):
+        raise KernelError("causal_conv: kept must be contiguous float32 [slots, taps - 1, channels]")
+    if out.dtype != torch.float32 or out.stride(-1) != 1 or out.shape[-1] < channels or out.shape[0] < n_tokens:
+        raise KernelError("causal_conv: out must be float32 [T, channels]")
+    rc = _lib().rb_causal_conv(_ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, col0, channels, taps, _ptr(weight),
+                               _f32vec(bias, channels, "causal_conv: bias"), UNIT_ACTS[act], _ptr(kept), _i32(seq_slot, "seq_slot"),
+                               _i32(cu_q, "cu_q"), n_seqs, max_q_len, _ptr(out), out.stride(0), _stream())
+    _check(rc, "causal_conv")
+
+
+@_profiled(lambda a, facts: (a["n_tokens"] * 4 * (a["u"].shape[1] + a["heads"] * a["p"]) + 8 * a["n_seqs"] * a["heads"] * a["n"] * a["p"],
+                             6 * a["n_tokens"] * a["heads"] * a["n"] * a["p"]))
+def ssm_scan(u: torch.Tensor, n_tokens: int, x_off: int, b_off: int, c_off: int, proj: torch.Tensor, dt_off: int,
+             dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor, heads: int, groups: int, n: int, p: int,
+             state: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, n_seqs: int, out: torch.Tensor):
+    """The step's tokens through S = exp(-exp(a_log[h]) dt) S + dt B x^T, y = S^T C + skip[h] x for every (sequence, head),
+    dt = softplus(raw + dt_bias[h]).  ``u`` float32 [T, >=]: x (heads * p columns from x_off), B and C (groups * n columns
+    from b_off and c_off; head h reads group h // (heads / groups)); raw: column dt_off + h of ``proj`` ([T, N] or partial
+    sums).  ``state`` float32 [slots, heads, n, p], read and written in place; ``out`` float32 [T, heads * p]."""
+    n_in, in_stride, row_stride = _partials(proj, "ssm_scan")
+    if u.dtype != torch.float32 or u.stride(-1) != 1 or max(b_off, c_off) + groups * n > u.shape[-1] or x_off + heads * p > u.shape[-1]:
+        raise KernelError("ssm_scan: u must be float32 rows that hold x, B and C")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, n, p):
+        raise KernelError("ssm_scan: state must be contiguous float32 [slots, heads, n, p]")
+    if out.dtype != torch.float32 or out.stride(-1) != 1 or out.shape[-1] != heads * p or out.shape[0] < n_tokens:
+        raise KernelError("ssm_scan: out must be float32 [T, heads * p]")
+    if dt_off + heads > proj.shape[-1] or heads % groups:
+        raise KernelError("ssm_scan: the step sizes must lie inside the projection rows, and groups divide heads")
+    rc = _lib().rb_ssm_scan(_ptr(u), u.stride(0), x_off, b_off, c_off, _ptr(proj), dtype_code(proj.dtype), n_in, in_stride,
+                            row_stride, dt_off, _f32vec(dt_bias, heads, "ssm_scan: dt_bias"), _f32vec(a_log, heads, "ssm_scan: a_log"),
+                            _f32vec(skip, heads, "ssm_scan: skip"), heads, groups, n, p, _ptr(state), _i32(seq_slot, "seq_slot"),
+                            _i32(cu_q, "cu_q"), n_seqs, _ptr(out), out.stride(0), _stream())
+    _check(rc, "ssm_scan")
+
+
+@_profiled(lambda a, facts: (a["n_tokens"] * a["y"].shape[1] * (4 + _esz(a["proj"]) * _n_in(a["proj"]) + _esz(a["out"])),
+                             a["n_tokens"] * a["y"].shape[1] * 8))
+def gate_group_norm(y: torch.Tensor, proj: torch.Tensor, z_off: int, weight: Optional[torch.Tensor], eps: float, groups: int,
+                    gate_act: str, out: torch.Tensor, slot_of_token: torch.Tensor, n_tokens: int):
+    """out [T, W] = rmsnorm over each of ``groups`` equal parts of (y * act(z)) (eps inside the root) (* weight float32 [W]):
+    the gate first, then the norm.  z: columns z_off .. z_off + W of ``proj`` (partial sums added first).  y float32."""
+    W = y.shape[1]
+    n_in, in_stride, row_stride = _partials(proj, "gate_group_norm")
+    if y.dtype != torch.float32 or y.stride(1) != 1 or out.stride(1) != 1 or out.shape[1] != W or z_off + W > proj.shape[-1] or W % groups:
+        raise KernelError("gate_group_norm: y must be float32 [T, W], out [T, W], the gate inside the projection rows")
+    rc = _lib().rb_gate_group_norm(_ptr(y), y.stride(0), _ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, z_off,
+                                   _f32vec(weight, W, "gate_group_norm: weight"), float(eps), groups, W, UNIT_ACTS[gate_act],
+                                   _ptr(out), dtype_code(out.dtype), out.stride(0), _i32(slot_of_token, "slot_of_token"),
+                                   n_tokens, _stream())
+    _check(rc, "gate_group_norm")
+
+
+# ---- latent attention with a query latent and a rotated key part ------------------------------------------------------------
+
+@_profiled(lambda a, facts: (a["n_tokens"] * ((a["q_rank"] + a["rank"] + a["rot"]) * (_esz(a["proj"]) * _n_in(a["proj"]) + _esz(a["cache"]))), 0))
+def latent_rot_prep(proj: torch.Tensor, n_tokens: int, q_rank: int, rank: int, rot: int, n_gate: int, q_norm_w: Optional[torch.Tensor],
+                    norm_w: torch.Tensor, eps: float, cq_out: Optional[torch.Tensor], gate_out: Optional[torch.Tensor],
+                    cache: torch.Tensor, cos_sin: Optional[torch.Tensor], positions: torch.Tensor, slot_of_token: torch.Tensor,
+                    block_table: torch.Tensor):
+    """proj rows = [query latent (q_rank) | latent (rank) | rotated key part (rot) | gate logits (n_gate)] ([T, N] or partial
+    sums).  The query latent, RMS-normalised with ``q_norm_w``, goes to ``cq_out`` [T, q_rank]; the latent, normalised with
+    ``norm_w``, then the key part turned by ``cos_sin`` (rotate-half pairs), then zeros go to the token's row of ``cache``
+    [pages, 1, 64, dp]; sigmoid of the gate logits to ``gate_out`` float32 [T, n_gate]."""
+    n_in, in_stride, row_stride = _partials(proj, "latent_rot_prep")
+    dp = cache.shape[-1]
+    if proj.shape[-1] < q_rank + rank + rot + n_gate or dp < rank + rot:
+        raise KernelError("latent_rot_prep: projection rows or cache rows are too narrow")
+    if tuple(cache.shape[1:3]) != (1, PAGE) or not cache.is_contiguous():
+        raise KernelError("latent_rot_prep: cache must be [pages, 1, 64, dp]")
+    if q_rank and (cq_out is None or cq_out.dtype != cache.dtype or cq_out.stride(-1) != 1 or cq_out.shape[-1] < q_rank):
+        raise KernelError("latent_rot_prep: cq_out must hold q_rank elements a row in the cache's type")
+    if n_gate and (gate_out is None or gate_out.dtype != torch.float32 or not gate_out.is_contiguous() or gate_out.shape[-1] != n_gate):
+        raise KernelError("latent_rot_prep: gate_out must be contiguous float32 [T, n_gate]")
+    if rot and (cos_sin is None or cos_sin.dtype != torch.float32 or not cos_sin.is_contiguous() or cos_sin.numel() < n_tokens * rot):
+        raise KernelError("latent_rot_prep: cos_sin must be float32 [T, rot / 2, 2]")
+    rc = _lib().rb_latent_rot_prep(
+        _ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, q_rank, rank, rot, n_gate,
+        _f32vec(q_norm_w, q_rank, "latent_rot_prep: q_norm_w") if q_rank else None, _f32vec(norm_w, rank, "latent_rot_prep: norm_w"),
+        float(eps), _ptr(cq_out), cq_out.stride(0) if cq_out is not None else 0, _ptr(gate_out), _ptr(cache), dp,
+        dtype_code(cache.dtype), _ptr(cos_sin), _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"),
+        _i32(block_table, "block_table"), block_table.shape[1], n_tokens, _stream())
+    _check(rc, "latent_rot_prep")
+
+
+@_profiled(lambda a, facts: (a["n_tokens"] * a["heads"] * (a["folded"].shape[-1] // a["heads"] - a["rank"]) * 2 * _esz(a["q"]), 0))
+def latent_q_rot(q: torch.Tensor, heads: int, dim: int, rot: int, rank: int, cos_sin: Optional[torch.Tensor], folded: torch.Tensor,
+                 slot_of_token: torch.Tensor, n_tokens: int):
+    """Head h of ``q`` [T, heads * (dim + rot)] is [dim plain | rot rotated]: the rotated entries, turned by ``cos_sin``
+    (rotate-half pairs), go to folded[t, h * dp + rank : + rot] and zeros behind them up to dp = folded.shape[-1] / heads."""
+    dp = folded.shape[-1] // heads
+    if q.dtype != folded.dtype or q.stride(-1) != 1 or folded.stride(-1) != 1 or q.shape[-1] < heads * (dim + rot) or dp < rank + rot:
+        raise KernelError("latent_q_rot: shapes or types do not fit")
+    rc = _lib().rb_latent_q_rot(_ptr(q), q.stride(0), heads, dim, rot, rank, dp, _ptr(cos_sin), _ptr(folded), folded.stride(0),
+                                dtype_code(q.dtype), _i32(slot_of_token, "slot_of_token"), n_tokens, _stream())
+    _check(rc, "latent_q_rot")
+
+
+# ---- attention with a norm over whole projections and head weights mixed after the softmax -----------------------------------
+
+@_profiled(lambda a, facts: (a["n_tokens"] * ((a["nq"] + a["nkv"]) * a["hd"] + a["nkv"] * a["vd"]) * (_esz(a["proj"]) * _n_in(a["proj"]) + _esz(a["q_out"])), 0))
+def wide_norm_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, n_tokens: int, nq: int, nkv: int, hd: int, vd: int, hdp: int,
+                         q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float, factor: Optional[torch.Tensor],
+                         cos_sin: Optional[torch.Tensor], rot_dim: int, interleaved: bool, positions: torch.Tensor,
+                         slot_of_token: torch.Tensor, block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor):
+    """proj rows = [q (nq * hd) | k (nkv * hd) | v (nkv * vd)] ([T, N] or partial sums).  q and k are RMS-normalised over their
+    whole width with ``q_norm_w`` / ``k_norm_w`` (float32, that wide; None: no norm), the first ``rot_dim`` entries of every
+    head turn by ``cos_sin`` (neighbouring pairs when ``interleaved``), query head h is multiplied by ``factor[h]``; q goes to
+    ``q_out`` [T, nq * hdp], k and v to their pages [pages, nkv, 64, hdp], heads padded with zeros."""
+    n_in, in_stride, row_stride = _partials(proj, "wide_norm_rope_cache")
+    if proj.shape[-1] < (nq + nkv) * hd + nkv * vd:
+        raise KernelError("wide_norm_rope_cache: projection rows are too narrow")
+    if q_out.stride(-1) != 1 or q_out.shape[-1] < nq * hdp or k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype:
+        raise KernelError("wide_norm_rope_cache: q_out rows must hold nq * hdp elements of the cache's type")
+    if tuple(k_cache.shape[1:]) != (nkv, PAGE, hdp) or k_cache.shape != v_cache.shape or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError("wide_norm_rope_cache: caches must be [pages, nkv, 64, hdp]")
+    if rot_dim and (cos_sin is None or cos_sin.dtype != torch.float32 or not cos_sin.is_contiguous() or cos_sin.numel() < n_tokens * rot_dim):
+        raise KernelError("wide_norm_rope_cache: cos_sin must be float32 [T, rot_dim / 2, 2]")
+    rc = _lib().rb_wide_norm_rope_cache(
+        _ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, nq, nkv, hd, vd, hdp,
+        _f32vec(q_norm_w, nq * hd, "wide_norm_rope_cache: q_norm_w"), _f32vec(k_norm_w, nkv * hd, "wide_norm_rope_cache: k_norm_w"),
+        float(eps), _f32vec(factor, nq, "wide_norm_rope_cache: factor"), _ptr(cos_sin) if rot_dim else None, rot_dim,
+        1 if interleaved else 0, _ptr(q_out), q_out.stride(0), _ptr(k_cache), _ptr(v_cache), dtype_code(q_out.dtype),
+        _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"), _i32(block_table, "block_table"),
+        block_table.shape[1], n_tokens, _stream())
+    _check(rc, "wide_norm_rope_cache")
+
+
+@_profiled(lambda a, facts: (a["n_tokens"] * a["nq"] * (a["nkv"] * a["hdp"] + a["vd"]) * _esz(a["o"]), 2 * a["n_tokens"] * a["nq"] * a["nq"] * a["vd"]))
+def talk_mix(o: torch.Tensor, mix: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hdp: int, vd: int, slot_of_token: torch.Tensor,
+             n_tokens: int):
+    """out[t, h, :vd] = sum_g mix[h, g] * o[t, pair(g, m(h)), :vd]: ``o`` [T, nq * nkv * hdp] holds, for every query head g and
+    stored value head m, head g's weights applied to m's values (pair (a, m) of key head a at a * nkv + m, its queries in
+    order); m(h) is head h's own key/value head; ``mix`` float32 [nq, nq]."""
+    if o.dtype != out.dtype or o.stride(-1) != 1 or out.stride(-1) != 1 or o.shape[-1] < nq * nkv * hdp or out.shape[-1] < nq * vd:
+        raise KernelError("talk_mix: shapes or types do not fit")
+    rc = _lib().rb_talk_mix(_ptr(o), o.stride(0), _f32vec(mix, nq * nq, "talk_mix: mix"), _ptr(out), out.stride(0), nq, nkv, hdp, vd,
+                            dtype_code(o.dtype), _i32(slot_of_token, "slot_of_token"), n_tokens, _stream())
+    _check(rc, "talk_mix")

@@ -14,11 +14,12 @@ from .mlp import GatedMLP
 from .latent_attention import LatentAttention
 from .routed_mlp import RoutedMLP
 from .linear_attention import LinearAttention
-from .block import ParallelBlock, PreNormBlock, SandwichNormBlock
+from .state_space import StateSpace
+from .block import ParallelBlock, PostNormBlock, PreNormBlock, SandwichNormBlock
 
 __all__ = [
     "BuildEnv", "DeferredNorm", "ResidualSink", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "build_block",
     "build_feed_forward", "build_mixer", "build_norm", "build_position", "register_arrangement",
     "register_feed_forward", "register_mixer", "register_norm", "register_position", "registered",
-    "Linear", "RMSNorm", "NoPosition", "RotaryNeox", "Attention", "GatedMLP", "PreNormBlock", "LatentAttention", "RoutedMLP", "SandwichNormBlock", "SinusoidPosition", "RotaryPairs", "LinearAttention", "ParallelBlock",
+    "Linear", "RMSNorm", "NoPosition", "RotaryNeox", "Attention", "GatedMLP", "PreNormBlock", "LatentAttention", "RoutedMLP", "SandwichNormBlock", "SinusoidPosition", "RotaryPairs", "LinearAttention", "ParallelBlock", "StateSpace", "PostNormBlock",
 ]

@@ -16,6 +16,11 @@ may stay visible to every later query; the softmax's denominator may have one mo
 that brings no value; queries and keys may be divided by their root mean square after the position
 encoding (``qk_unit_norm``); biases may be given for some of the projections only; and the values that
 a layer caches may be blended with those of an earlier layer of the same step (``value_mix``).
+Three more parameters form one path of their own (``_forward_wide``): ``qk_norm`` "whole" (queries and keys are each
+normalised over ALL their heads together, with a weight vector of that width, before the position encoding),
+``head_temperature`` (query head n's scores are multiplied by a number of the layer, folded into the query) and
+``talking_heads`` (after the softmax the heads' weights are mixed by a matrix of the layer, a'_n = sum_g M[n, g] a_g,
+and head n applies a'_n to the values of its own key/value head).
 Heads of unequal or odd sizes are written into the cache padded with zeros to one width that the
 attention kernels take: zeros in queries and keys change no score, zeros in values give zeros
 that are dropped before the output projection.
@@ -45,7 +50,7 @@ PROMPT_FUSED_MIN_TOKENS = 4096
 # Tensor-name stems by role, unless the spec's ``names`` says otherwise (the defaults are those of
 # Hugging Face's Qwen3 checkpoints: rocml/src/weights/layer.rs:47-58 lists the same tensors under GGUF names).
 TENSOR_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm",
-                "gate": "gate_proj", "value_mix": "value_mix"}
+                "gate": "gate_proj", "value_mix": "value_mix", "talk": "head_mix", "temperature": "head_temperature"}
 
 VALUE_MIX_SOURCE = "attention.value_mix_source"    # where a step keeps the source layer's values (StepBatch.scratch)
 
@@ -74,6 +79,10 @@ class Attention(Mixer):
         bias = p.get("bias", False)
         self.bias = bool(bias)
         self.qk_norm = bool(p.get("qk_norm", False))
+        self.qk_norm_whole = p.get("qk_norm") == "whole"
+        self.head_temperature = bool(p.get("head_temperature", False))
+        self.talking_heads = bool(p.get("talking_heads", False))
+        self.wide = self.qk_norm_whole or self.head_temperature or self.talking_heads
         self.qk_norm_eps = float(p.get("qk_norm_eps", 1e-6))
         self.qk_unit_norm = bool(p.get("qk_unit_norm", False))
         self.window = p.get("window")
@@ -87,13 +96,19 @@ class Attention(Mixer):
             raise ConfigError("attention: keep_first counts positions and cannot be negative")
         if self.window and self.chunk:
             raise ConfigError("attention: a layer has a window or blocks of positions, not both")
+        if self.wide and (self.gated or self.keep_first or self.sink is not None or self.qk_unit_norm or self.value_mix or
+                          (self.qk_norm and not self.qk_norm_whole) or p.get("shares_cache")):
+            raise ConfigError("attention: a norm over whole projections, head temperatures and mixed heads do not combine with "
+                              "gates, kept first keys, a sink, unit norms, blended values, per-head norms or a shared cache")
+        if self.talking_heads and self.nkv * self.nq * self.hdp > 65535 * 16:
+            raise ConfigError("attention: too many heads to mix")
         if (self.window is not None and int(self.window) < 1) or (self.chunk is not None and int(self.chunk) < 1):
             raise ConfigError("attention: a window or a block of positions holds at least one position")
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
         self.shares_cache = bool(p.get("shares_cache", False))  # set by the model for a reading layer
         self.position = build_position(spec.position, self.hd, env)
         # the plain layout: equal head sizes that the kernels take as they are, rotate-half pairs, no gate
-        self.plain = self.vd == self.hd == self.hdp and not self.gated and \
+        self.plain = not self.wide and self.vd == self.hd == self.hdp and not self.gated and \
             not (self.position.inv_freq is not None and getattr(self.position, "interleaved", False)) and \
             not (self.keep_first or self.sink is not None or self.qk_unit_norm or self.value_mix)
         if not self.plain and self.shares_cache:
@@ -121,6 +136,8 @@ class Attention(Mixer):
         self.q_norm_w: Optional[torch.Tensor] = None
         self.k_norm_w: Optional[torch.Tensor] = None
         self.v_lambda: Optional[torch.Tensor] = None     # float32 [1] on the device: the share of the source layer's values
+        self.talk: Optional[torch.Tensor] = None         # float32 [nq, nq]: the matrix that mixes the heads' weights
+        self.temperature: Optional[torch.Tensor] = None  # float32 [nq]: a factor on every head's scores
 
     def cache_requirement(self):
         return KVRequirement(self.nkv, self.hdp, self.window, chunk=self.chunk, keep_first=self.keep_first)
@@ -133,10 +150,17 @@ class Attention(Mixer):
 
     def declare(self, prefix: str) -> List[TensorDecl]:
         out = self.qkv.declare(prefix) + self.o.declare(prefix)
-        if self.qk_norm:
+        if self.qk_norm_whole:
+            out.append(TensorDecl(f"{prefix}{self.names['q_norm']}.weight", (self.nq * self.hd,), "norm"))
+            out.append(TensorDecl(f"{prefix}{self.names['k_norm']}.weight", (self.nkv * self.hd,), "norm"))
+        elif self.qk_norm:
             out.append(TensorDecl(f"{prefix}{self.names['q_norm']}.weight", (self.hd,), "norm"))
             if not self.shares_cache:
                 out.append(TensorDecl(f"{prefix}{self.names['k_norm']}.weight", (self.hd,), "norm"))
+        if self.talking_heads:
+            out.append(TensorDecl(f"{prefix}{self.names['talk']}.weight", (self.nq, self.nq), "mixing"))
+        if self.head_temperature:
+            out.append(TensorDecl(f"{prefix}{self.names['temperature']}.weight", (self.nq,), "norm"))
         if self.value_mix == "mix":
             out.append(TensorDecl(f"{prefix}{self.names['value_mix']}.weight", (), "fraction"))
         return out
@@ -150,7 +174,14 @@ class Attention(Mixer):
         if not self.plain:
             self.qkv.pad_rows(8)     # a stack with a few gate rows is rarely a multiple of 8 wide
         self.o.load(tensors, prefix)
-        if self.qk_norm:
+        if self.talking_heads:
+            self.talk = tensors[f"{prefix}{self.names['talk']}.weight"].float().contiguous()
+        if self.head_temperature:
+            self.temperature = tensors[f"{prefix}{self.names['temperature']}.weight"].float().contiguous()
+        if self.qk_norm_whole:         # 32-bit vectors, as the kernel of this path reads them
+            self.q_norm_w = tensors[f"{prefix}{self.names['q_norm']}.weight"].float().contiguous()
+            self.k_norm_w = tensors[f"{prefix}{self.names['k_norm']}.weight"].float().contiguous()
+        elif self.qk_norm:
             self.q_norm_w = tensors[f"{prefix}{self.names['q_norm']}.weight"]
             self.k_norm_w = self.q_norm_w if self.shares_cache else tensors[f"{prefix}{self.names['k_norm']}.weight"]
             if self.k_norm_w.dtype != self.q_norm_w.dtype:
@@ -195,6 +226,8 @@ class Attention(Mixer):
         qd = self.nq * self.hd
         window = self._span()
         writes = view.writes and not self.shares_cache
+        if self.wide:
+            return self._forward_wide(xn, batch, view, window, sink, add_into)
         if not self.plain:
             return self._forward_padded(xn, batch, view, window, writes, sink, add_into)
         attn = torch.empty((T, qd), dtype=act, device=dev)
@@ -280,6 +313,41 @@ class Attention(Mixer):
             attn = narrow
         return self._project_out(attn, T, sink, add_into)
 
+    def _forward_wide(self, xn, batch, view, window, sink, add_into):
+        """A norm over the whole q and k projections, a temperature per head, the heads' weights mixed after the softmax.
+
+        One kernel normalises, rotates, scales and pads the queries and writes keys and values to their pages.  Mixing
+        weights and then applying them to values is the same as applying every head's own weights to the values of every
+        stored head and then mixing the results: o_n = sum_g M[n, g] (a_g . V_m(n)).  So the attention runs once over
+        (key head, value head) pairs (``cross``), and a small kernel forms the sums over g in 32-bit."""
+        T = batch.n_tokens
+        dev, act = self.env.device, self.env.act_dtype
+        if isinstance(xn, DeferredNorm):
+            xn = xn.materialize()
+        proj = self.qkv.forward_auto(xn, T)
+        rot = self.position.rot_dim if self.position.inv_freq is not None else 0
+        q = torch.empty((T, self.nq * self.hdp), dtype=act, device=dev)
+        with scope(op="rotate_cache"):
+            kernels.wide_norm_rope_cache(proj, q, T, self.nq, self.nkv, self.hd, self.vd, self.hdp, self.q_norm_w, self.k_norm_w,
+                                         self.qk_norm_eps, self.temperature, self.position.cos_sin(batch) if rot else None, rot,
+                                         getattr(self.position, "interleaved", False), batch.positions, batch.slot_of_token,
+                                         view.block_table, view.k, view.v)
+        pairs = self.nkv if self.talking_heads and self.nkv > 1 else 1
+        wide = torch.empty((T, self.nq * pairs * self.hdp), dtype=act, device=dev)
+        paged_attention(q, wide, batch, view.k, view.v, view.block_table, self.nq * pairs, self.nkv * pairs, self.hdp, self.scale,
+                        window, cross=pairs if pairs > 1 else 0)
+        if self.talking_heads:
+            attn = torch.empty((T, self.nq * self.vd), dtype=act, device=dev)
+            with scope(op="mix_heads"):
+                kernels.talk_mix(wide, self.talk, attn, self.nq, self.nkv, self.hdp, self.vd, batch.slot_of_token, T)
+        elif self.hdp != self.vd:
+            attn = torch.empty((T, self.nq * self.vd), dtype=act, device=dev)
+            with scope(op="head_gate"):
+                kernels.head_gate(wide, attn, None, self.nq, self.hdp, self.vd, T)
+        else:
+            attn = wide
+        return self._project_out(attn, T, sink, add_into)
+
     def _project_out(self, attn, T, sink, add_into):
         if sink is not None:
             deferred = self.o.forward_residual(attn, T, sink)
@@ -348,14 +416,19 @@ class Attention(Mixer):
         paged_attention(q, out, batch, view.k, view.v, view.block_table, self.nq, self.nkv, self.hd, self.scale, window)
 
 
-def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window, keep=0, sink=None, gate=None) -> bool:
+def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window, keep=0, sink=None, gate=None,
+                    cross=0) -> bool:
     """Softmax attention of the step's queries (rows of nq heads of ``hd``) over paged keys and values
     [pages, nkv, 64, hd], causal, inside ``window`` when it is not 0 (and the first ``keep`` positions beside it);
     ``sink``: a score whose exponential joins every row's denominator.  One token per sequence:
     keys split in fixed chunks, partial results merged; otherwise whole rows.  Any mixer whose cache is
     such pages calls this (keys and values may be the same tensor).  ``gate``: nq * hd columns of the step's projection
     rows ([T, ..] or partial sums [S, T, ..]); a kernel that takes them multiplies its result by their sigmoid.
-    Returns whether that was done: if not, the result is as without ``gate`` and the caller gates it."""
+    Returns whether that was done: if not, the result is as without ``gate`` and the caller gates it.
+    ``cross`` (n > 1, the cache's own number of key/value heads): every query head's weights are applied to the values of
+    every stored head; nkv = n * n then counts (key head, value head) pairs and nq = n * query heads the results."""
+    if cross > 1:
+        return _paged_attention_pairs(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window, cross)
     if batch.is_decode:
         chunk = DECODE_CHUNK
         T = batch.n_tokens
@@ -397,4 +470,23 @@ def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, s
     kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                               batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
                               scale, window, keep=keep, sink=sink)
+    return False
+
+
+def _paged_attention_pairs(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window, cross) -> bool:
+    """``paged_attention`` over (key head, value head) pairs: the plain kernel, which reads a pair's keys and values from
+    two stored heads; one token a sequence splits the keys in fixed chunks and merges, as always."""
+    if batch.is_decode:
+        chunk = DECODE_CHUNK
+        T = batch.n_tokens
+        n_chunks = max(1, (batch.max_kv_len + chunk - 1) // chunk)
+        if n_chunks > 1:
+            acc = torch.empty((T, nq, n_chunks, hd), dtype=torch.float32, device=q.device)
+            ml = torch.empty((T, nq, n_chunks, 2), dtype=torch.float32, device=q.device)
+            kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q, batch.kv_len,
+                                      batch.n_seqs, 1, nq, nkv, hd, scale, window, chunk, n_chunks, acc, ml, cross=cross)
+            kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, nq, hd, chunk, n_chunks, window)
+            return False
+    kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q, batch.kv_len, batch.n_seqs,
+                              batch.max_q_len, nq, nkv, hd, scale, window, cross=cross)
     return False

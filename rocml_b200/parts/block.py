@@ -342,3 +342,174 @@ class ParallelTwoNormsBlock(ParallelBlock):
             if isinstance(xn, DeferredNorm):
                 xn = xn.materialize()
             return xn, self.ff_norm.forward(resid, None, T)
+
+
+POST_NORM_NAMES = {"mixer_scale": "mixer_scale", "ff_scale": "ff_scale", "shift": "shift"}
+
+
+@register_arrangement("post_norm")
+class PostNormBlock:
+    """x <- norm1(alpha x + g1 * mixer(h)); x <- norm2(alpha x + g2 * ff(x)): the norm follows the sum, so the 32-bit
+    stream IS the normalised row and the sublayers read it as it is.
+
+    Parameters (``LayerSpec.arrangement_params``): ``alpha``, the factor on the stream inside the sum; ``layer_scale``:
+    each sublayer's result is multiplied, element by element, by a vector of the layer before it joins the sum;
+    ``token_shift``: the mixer reads h_t = x_t + (x_(t-1) - x_t) * mu instead of x_t, mu a vector of the layer and
+    x_(t-1) the row of the token before in the same sequence (zeros before the first); the last row of every step
+    is kept per sequence, as a state of the layer beside whatever its mixer keeps (``cache_requirement``).
+
+    One kernel does a sublayer's sum and norm (``kernels.postln``): it adds the result's partial sums in their order,
+    applies the vector, alpha and the norm in 32-bit, writes the stream in place and, when a product reads the row
+    next, the row in the activations' type as well.  One kernel blends the rows for the mixer and hands the
+    kept row over.  Nothing is left pending for the layer after it.  A layer without a feed-forward has only the
+    first half."""
+
+    chains = False
+
+    def __init__(self, spec: LayerSpec, hidden: int, env: BuildEnv, mixer_spec=None):
+        from ..config.specs import tensor_names
+        from ..errors import ConfigError
+        p = spec.arrangement_params
+        unknown = sorted(set(p) - {"alpha", "layer_scale", "token_shift", "names"})
+        if unknown:
+            raise ConfigError(f"post_norm: unknown parameters {unknown}")
+        self.spec = spec
+        self.prefix = spec.prefix
+        self.env = env
+        self.hidden = hidden
+        self.alpha = float(p.get("alpha", 1.0))
+        self.layer_scale = bool(p.get("layer_scale", False))
+        self.token_shift = bool(p.get("token_shift", False))
+        try:
+            self.names = tensor_names(p, POST_NORM_NAMES)
+        except ValueError as e:
+            raise ConfigError(f"post_norm: {e}") from None
+        self.mixer_norm = build_norm(spec.mixer_norm, hidden, env)
+        self.mixer = build_mixer(mixer_spec or spec.mixer, hidden, env)
+        self.ff = self.ff_norm = None
+        if spec.feed_forward is not None:
+            self.ff_norm = build_norm(spec.ff_norm, hidden, env)
+            self.ff = build_feed_forward(spec.feed_forward, hidden, env)
+        for n in (self.mixer_norm, self.ff_norm):
+            if n is not None and (not hasattr(n, "eps") or getattr(n, "offset", 0.0)):
+                raise ConfigError("post_norm is built for norms with a plain weight vector and an eps (rmsnorm)")
+        self.mixer_gain = self.ff_gain = self.mu = None
+        self._w1 = self._w2 = None
+
+    def _parts(self):
+        p, s = self.prefix, self.spec
+        out = [(self.mixer_norm, f"{p}.{s.mixer_norm_name}"), (self.mixer, f"{p}.{s.mixer_name}")]
+        if self.ff is not None:
+            out += [(self.ff_norm, f"{p}.{s.ff_norm_name}"), (self.ff, f"{p}.{s.ff_name}")]
+        return out
+
+    def _own(self):
+        """(attribute, tensor name) of the arrangement's own vectors."""
+        out = []
+        if self.layer_scale:
+            out.append(("mixer_gain", f"{self.prefix}.{self.names['mixer_scale']}.weight"))
+            if self.ff is not None:
+                out.append(("ff_gain", f"{self.prefix}.{self.names['ff_scale']}.weight"))
+        if self.token_shift:
+            out.append(("mu", f"{self.prefix}.{self.names['shift']}.weight"))
+        return out
+
+    def declare(self) -> List[TensorDecl]:
+        return [d for part, name in self._parts() for d in part.declare(name)] + \
+            [TensorDecl(name, (self.hidden,), "norm") for _, name in self._own()]
+
+    def ignorable(self) -> List[str]:
+        out = [n for part, name in self._parts() for n in getattr(part, "ignorable", lambda prefix: [])(name)]
+        if self.ff is None:        # a layer without a feed-forward may still carry the second half's vectors
+            out += [f"{self.prefix}.{self.spec.ff_norm_name}.weight", f"{self.prefix}.{self.names['ff_scale']}.weight"]
+        return out
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for part, name in self._parts():
+            part.load(tensors, name)
+        for attr, name in self._own():
+            setattr(self, attr, tensors[name].float().contiguous())      # 32-bit: they enter the stream's sum
+        self._w1 = self.mixer_norm.weight.float().contiguous()
+        self._w2 = self.ff_norm.weight.float().contiguous() if self.ff_norm is not None else None
+
+    def cache_requirement(self):
+        from ..cache.requirements import BundleRequirement, StateRequirement
+        req = self.mixer.cache_requirement()
+        if not self.token_shift:
+            return req
+        return BundleRequirement.of(req, shift=StateRequirement((self.hidden,), torch.float32))
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for part, _ in self._parts())
+
+    def weight_bytes(self) -> int:
+        own = sum(self.hidden * 4 for _ in self._own())
+        return sum(part.weight_bytes() for part, _ in self._parts()) + own
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        esz = 4 if self.env.mode == "float32" else 2
+        rows = n_tokens * self.hidden * esz
+        return rows + max(self.mixer.workspace_bytes(n_tokens), self.ff.workspace_bytes(n_tokens) if self.ff is not None else 0)
+
+    def cost(self, q_lens, kv_lens):
+        parts = [part.cost(q_lens, kv_lens) for part, _ in self._parts()]
+        return sum(p[0] for p in parts), sum(p[1] for p in parts)
+
+    def _rows_for(self, resid, T):
+        """The stream's rows as a product reads them: themselves in 32-bit mode, a copy in the activations' type otherwise."""
+        from .. import kernels
+        if self.env.act_dtype == torch.float32:
+            return resid
+        out = torch.empty((T, self.hidden), dtype=self.env.act_dtype, device=resid.device)
+        kernels.cast(resid[:T], out)
+        return out
+
+    def _join(self, resid, pending):
+        """Whatever a layer of another kind left pending joins the stream first."""
+        from .. import kernels
+        if pending is None or isinstance(pending, DeferredNorm):
+            return
+        for d in (pending if isinstance(pending, (tuple, list)) else (pending,)):
+            if isinstance(d, RoutedRows):
+                d = d.materialize()
+            if d is not None:
+                kernels.residual_inject(resid, d)
+
+    def forward(self, resid, pending, batch, view):
+        from .. import kernels
+        T = batch.n_tokens
+        act = self.env.act_dtype
+        self._join(resid, pending)
+        if self.token_shift:
+            h = torch.empty((T, self.hidden), dtype=act, device=resid.device)
+            with scope(op="token_shift"):
+                kernels.token_shift(resid, self.mu, view.extras["shift"].state, batch.seq_slot, batch.cu_q, batch.n_seqs,
+                                    batch.max_q_len, h, T)
+        else:
+            with scope(op="mixer_input"):
+                h = self._rows_for(resid, T)
+        delta = self.mixer.forward(h, batch, view)
+        delta = _as_partial_sums(delta, T)
+        rows = None
+        if self.ff is not None and act != torch.float32:
+            rows = torch.empty((T, self.hidden), dtype=act, device=resid.device)
+        with scope(op="mixer_post_norm"):
+            kernels.postln(resid, delta, self.mixer_gain, self._w1, self.alpha, self.mixer_norm.eps, rows, batch.slot_of_token, T)
+        if self.ff is None:
+            return None
+        delta = _as_partial_sums(self.ff.forward(rows if rows is not None else resid, batch), T)
+        with scope(op="ff_post_norm"):
+            kernels.postln(resid, delta, self.ff_gain, self._w2, self.alpha, self.ff_norm.eps, None, batch.slot_of_token, T)
+        return None
+
+
+def _as_partial_sums(delta, n_rows: int):
+    """A sublayer's result in the form the sum's kernel adds: float32 [S, >= rows, H]."""
+    if isinstance(delta, RoutedRows):
+        delta = delta.materialize()
+    if delta is None or _is_partial_sums(delta, n_rows):
+        return delta
+    if isinstance(delta, torch.Tensor) and delta.dim() == 2:
+        delta = delta.unsqueeze(0)
+    return delta.float().contiguous()

@@ -10,7 +10,7 @@ class TensorDecl:
     """One tensor of the weight files.
 
     role: "matrix" (a linear weight or an embedding table, [out, in]),
-    "norm" (a norm's scale vector), "bias", "int_table" (integer table), "fraction" (a blend's share), or
+    "norm" (a norm's scale vector), "bias", "int_table" (integer table), "fraction" (a blend's share), "mixing" (a square matrix near the identity), or
     "state" (anything else a part defines; initialised like a matrix).
     """
 

@@ -3,7 +3,7 @@
 The reference has no such mode (it always opens a checkpoint); benchmarks and
 tests here need one because no checkpoint can be fetched.  Distributions: linear
 weights and embeddings N(0, 0.02); norm scales 1 + N(0, 0.1); biases N(0, 0.02); a fraction
-(a blend's share) 0.5 + N(0, 0.15).
+(a blend's share) 0.5 + N(0, 0.15); a mixing matrix (square) the identity + N(0, 0.1).
 Each tensor's values depend only on (seed, tensor name), never on the order in
 which tensors are produced, and are rounded to bfloat16 so that the 32-bit and
 the bfloat16 paths see exactly the same numbers.
@@ -36,6 +36,8 @@ def random_tensor(decl: TensorDecl, seed: int, device="cpu", dtype=torch.bfloat1
         x.mul_(0.1).add_(1.0)
     elif decl.role == "fraction":
         x.mul_(0.15).add_(0.5)
+    elif decl.role == "mixing":
+        x.mul_(0.1).add_(torch.eye(decl.shape[0], decl.shape[1], device=device))
     else:
         x.mul_(0.02)
     return x.to(dtype)

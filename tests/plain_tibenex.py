@@ -102,7 +102,7 @@ def latent_attention(h, positions, m, w, eps):
     """m: the mixer's sizes; w: its tensors by short name."""
     T = h.shape[0]
     H, dim, rd, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    rot = dict(m["rot"], dims=rd)
+    rot = dict(m.get("rot") or {"base": 10000.0}, dims=rd)
     cq = norm(h @ w["dq"].T, w["dq.norm"], eps)
     q = (cq @ w["uq"].T).reshape(T, H, dim + rd)
     dkv = h @ w["dkv"].T
@@ -124,8 +124,9 @@ def attention(h, positions, m, w, eps):
     q = norm(h @ w["q"].T, w["q.norm"], eps).reshape(T, H, dim)
     k = norm(h @ w["k"].T, w["k.norm"], eps).reshape(T, G, dim)
     v = (h @ w["v"].T).reshape(T, G, vd)
-    q = rotate(q, positions, m["rot"], "neighbours")
-    k = rotate(k, positions, m["rot"], "neighbours")
+    if m.get("rot") is not None:
+        q = rotate(q, positions, m["rot"], "neighbours")
+        k = rotate(k, positions, m["rot"], "neighbours")
     kv_of = torch.arange(H) // (H // G)
     s = torch.einsum("ihd,jhd->hij", q, k[:, kv_of]) * m["scale"] * w["temp"].reshape(H, 1, 1)
     a = causal_softmax(s, positions)

@@ -316,3 +316,92 @@ def write_safesun(folder, cfg_dict, seed, std=0.06):
         w[k] = t.to(torch.bfloat16)
     save_file(w, path)
     return folder
+
+
+# ---- Tibenex: layers that normalise after the sum; a state-space mixer, latent attention with a rotated part, attention
+# whose heads' weights are mixed -------------------------------------------------------------------------------------------
+def _t(kind, mixer, ff):
+    return {"type": kind, "mixer": mixer, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def _ssm(heads, vdim, state, groups, conv, norm_groups):
+    return {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": norm_groups}
+
+
+def _tlat(heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, rot):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "scale": scale}
+    if rot is not None:
+        m["rot"] = {"base": rot[0], "dims": rot_dim}
+        if len(rot) > 1:
+            m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), rot[1]))
+    return m
+
+
+def _tattn(heads, kv_heads, dim, vdim, scale, rot):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if rot is not None:
+        m["rot"] = {"base": rot[0], "dims": rot[1]}
+    return m
+
+
+# TA: every mixer once and the state-space mixer twice with different sizes; a layer without feed-forward
+TIBENEX_A = {
+    "architecture": "Tibenex", "vocab": 211, "width": 64, "norm": {"eps": 1e-6}, "postln_alpha": 1.7, "embedding": {"scale": 3.0},
+    "layers": [_t("mamba2", _ssm(4, 16, 8, 2, 4, 2), 96),
+               _t("attention", _tattn(4, 2, 16, 16, 0.3, (10000.0, 8)), None),
+               _t("latent_attention", _tlat(4, 16, 8, 24, 24, 40, 0.25, (1000.0, (4.0, 64, 8.0, 1.0))), 52),
+               _t("mamba2", _ssm(3, 20, 12, 1, 2, 1), 40)],
+}
+# TB: head sizes that the bfloat16 attention kernels take (a cached row of 96 + 32 = 128; heads of 64), one key/value head
+# (nothing to cross), as many key/value heads as query heads with value heads wider than key heads, a rotation of the whole
+# head and none at all, as many groups as heads, alpha 1
+TIBENEX_B = {
+    "architecture": "Tibenex", "vocab": 333, "width": 128, "norm": {"eps": 1e-5}, "postln_alpha": 1.0, "embedding": {"scale": 1.0},
+    "layers": [_t("latent_attention", _tlat(8, 32, 32, 64, 96, 64, 0.1, (500000.0,)), 160),
+               _t("attention", _tattn(8, 1, 64, 64, 0.12, (1000000.0, 64)), 64),
+               _t("mamba2", _ssm(8, 64, 64, 8, 3, 8), None),
+               _t("attention", _tattn(6, 6, 32, 48, 0.2, None), 96)],
+}
+# TC: sizes that are multiples of four only; one head; a convolution of one tap (nothing to keep); a latent without a
+# rotated part; a tiny plain part beside a larger rotated one; three query heads a key/value head; a large alpha
+TIBENEX_C = {
+    "architecture": "Tibenex", "vocab": 97, "width": 72, "norm": {"eps": 3e-5}, "postln_alpha": 4.0, "embedding": {"scale": 0.5},
+    "layers": [_t("mamba2", _ssm(1, 36, 5, 1, 1, 3), 28),
+               _t("latent_attention", _tlat(3, 20, 0, 12, 20, 12, 0.4, None), None),
+               _t("attention", _tattn(9, 3, 12, 20, 0.5, (300.0, 4)), 52),
+               _t("latent_attention", _tlat(5, 4, 12, 8, 36, 100, 0.3, (50.0, (3.0, 32, 4.0, 0.5))), 20),
+               _t("mamba2", _ssm(6, 4, 40, 3, 7, 6), None)],
+}
+TIBENEX = {"TA": TIBENEX_A, "TB": TIBENEX_B, "TC": TIBENEX_C}
+
+
+def write_tibenex(folder, cfg_dict, seed, std=0.06, slow_decay=False):
+    """A Tibenex model folder with random weights: matrices of standard deviation ``std``; norm weights, layer scales and
+    temperatures around one; the blend with the token before between 0 and 1; mixing matrices far from the identity; step
+    sizes and decays such that the state remembers tens of tokens (``slow_decay``: hundreds)."""
+    from safetensors.torch import load_file, save_file
+    write_model(folder, cfg_dict, seed)
+    path = os.path.join(folder, "model.safetensors")
+    w = load_file(path)
+    g = torch.Generator().manual_seed(seed)
+    for k in sorted(w):
+        t = w[k].float()
+        if k.endswith(".talk"):
+            t = torch.eye(t.shape[0]) * 0.7 + 0.3 * torch.randn(t.shape, generator=g)
+        elif k.endswith(".conv"):
+            t = t * 15.0
+        elif t.dim() == 2:
+            t = t * (std / 0.02)
+        elif k.endswith(".shift"):
+            t = torch.rand(t.shape, generator=g)
+        elif k.endswith((".ls1", ".ls2", ".temp", ".D")):
+            t = 1.0 + 3.0 * (t - 1.0)
+        elif k.endswith(".A_log"):
+            t = (t - 1.0) * 5.0 - (5.0 if slow_decay else 1.5)
+        elif k.endswith(".dt_bias"):
+            t = (t - 1.0) * 5.0 - 1.0
+        elif k.endswith(".conv.b"):
+            t = t * 5.0
+        w[k] = t.to(torch.bfloat16)
+    save_file(w, path)
+    return folder

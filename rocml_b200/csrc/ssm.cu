@@ -176,6 +176,215 @@ ssm_scan_kernel(const float* __restrict__ u, int ld_u, int x_off, int b_off, int
         if (jj < vt) st[(size_t)i * p + jj] = S[idx];
     }
 }
+// ---- prompts: the same recurrence by blocks of 64 tokens, all blocks at once ------------------------------------------------
+constexpr int CB = 64;              // tokens a block
+constexpr int CT = 256;             // threads: a 16 x 16 grid, each thread a 4 x 4 tile of a 64 x 64 result
+constexpr int CP = 64;              // columns of the state a block of the grid takes
+constexpr int CN = 64;              // rows of the state staged at a time
+constexpr int CL = CB + 4;          // row length of the transposed tiles (a multiple of 4 that is no multiple of 32)
+
+// Which sequence and which of its blocks of tokens the grid's block `g` is (blocks are numbered sequence after sequence).
+__device__ __forceinline__ bool find_tokens(int g, const int* seq_slot, const int* cu_q, int n_seqs, int* t0, int* m, int* slot) {
+    int base = 0;
+    for (int b = 0; b < n_seqs; ++b) {
+        const int n = cu_q[b + 1] - cu_q[b];
+        const int nb = seq_slot[b] >= 0 ? (n + CB - 1) / CB : 0;
+        if (g < base + nb) {
+            const int c = g - base;
+            *t0 = cu_q[b] + c * CB; *m = min(CB, n - c * CB); *slot = seq_slot[b];
+            return true;
+        }
+        base += nb;
+    }
+    return false;
+}
+
+// The block's step sizes and the running sums of its log decays: dt[t], cum[t] = sum_{r <= t} -rate * dt[r]; rows past m
+// repeat the last sum and have step size 0.
+template <typename IT>
+__device__ __forceinline__ void block_steps(const IT* raw, int n_in, size_t in_stride, int row_stride, int col, int t0, int m,
+                                            float rate, float bias, float* dt, float* cum, float* la) {
+    const int t = threadIdx.x;
+    if (t < CB) {
+        float d = 0.f;
+        if (t < m) d = softplus_f32(sum_in(raw + (size_t)(t0 + t) * row_stride + col, n_in, in_stride) + bias);
+        dt[t] = d;
+        la[t] = -rate * d;
+    }
+    __syncthreads();
+    if (t < CB) {
+        float c = 0.f;
+        for (int r = 0; r <= t; ++r) c += la[r];
+        cum[t] = c;
+    }
+    __syncthreads();
+}
+
+// acc[4][4] += A^T[k][rows] . B[k][cols] over k < K: At is [K][lda] (the thread's rows at 4 * ty), Bm is [K][ldb].
+__device__ __forceinline__ void tile_mm(float (&acc)[4][4], const float* At, int lda, const float* Bm, int ldb, int K, int ty, int tx) {
+#pragma unroll 4
+    for (int k = 0; k < K; ++k) {
+        const float4 a = *reinterpret_cast<const float4*>(At + k * lda + 4 * ty);
+        const float4 b = *reinterpret_cast<const float4*>(Bm + k * ldb + 4 * tx);
+        const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+}
+
+// (1) every block's own sum: L[n][p] = sum_s e^(cum_last - cum_s) dt_s B_s[n] x_s[p]; and e^(cum_last) per (block, head).
+template <typename IT>
+__global__ void __launch_bounds__(CT)
+ssm_block_sum_kernel(const float* __restrict__ u, int ld_u, int x_off, int b_off, const IT* __restrict__ raw, int n_in,
+                     size_t in_stride, int row_stride, int dt_off, const float* __restrict__ dt_bias,
+                     const float* __restrict__ a_log, int heads, int groups, int n, int p, const int* __restrict__ seq_slot,
+                     const int* __restrict__ cu_q, int n_seqs, float* __restrict__ work, float* __restrict__ block_decay) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ __align__(16) float Bw[CB][CN];        // [s][n]: B_s[n] * w_s
+    __shared__ __align__(16) float Xs[CB][CP];        // [s][p]
+    __shared__ float dt[CB], cum[CB], la[CB];
+    int t0, m, slot;
+    if (!find_tokens(blockIdx.z, seq_slot, cu_q, n_seqs, &t0, &m, &slot)) return;
+    const int h = blockIdx.y, p0 = blockIdx.x * CP, g = h / (heads / groups);
+    block_steps(raw, n_in, in_stride, row_stride, dt_off + h, t0, m, expf(a_log[h]), dt_bias[h], dt, cum, la);
+    const float last = cum[CB - 1];
+    if (threadIdx.x == 0 && blockIdx.x == 0) block_decay[(size_t)blockIdx.z * heads + h] = expf(last);
+    for (int idx = threadIdx.x; idx < CB * CP; idx += CT) {
+        const int s = idx / CP, j = idx - s * CP;
+        Xs[s][j] = (s < m && p0 + j < p) ? u[(size_t)(t0 + s) * ld_u + x_off + (size_t)h * p + p0 + j] : 0.f;
+    }
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float* dst = work + (((size_t)blockIdx.z * heads + h) * n) * p;
+    for (int n0 = 0; n0 < n; n0 += CN) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < CB * CN; idx += CT) {
+            const int s = idx / CN, i = idx - s * CN;
+            Bw[s][i] = (s < m && n0 + i < n) ? u[(size_t)(t0 + s) * ld_u + b_off + (size_t)g * n + n0 + i] * expf(last - cum[s]) * dt[s] : 0.f;
+        }
+        __syncthreads();
+        float acc[4][4] = {};
+        tile_mm(acc, &Bw[0][0], CN, &Xs[0][0], CP, CB, ty, tx);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int row = n0 + 4 * ty + i, col = p0 + 4 * tx + j;
+                if (row < n && col < p) dst[(size_t)row * p + col] = acc[i][j];
+            }
+    }
+}
+
+// (2) along each sequence: the state every block starts from takes the place of the block's own sum; the slot receives the
+// state after the last block.  Elementwise; a thread walks its element through the sequence's blocks.
+__global__ void __launch_bounds__(256)
+ssm_block_states_kernel(float* __restrict__ work, const float* __restrict__ block_decay, float* __restrict__ state, int heads,
+                        int np, const int* __restrict__ seq_slot, const int* __restrict__ cu_q) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    int first = 0;
+    for (int i = 0; i < b; ++i) first += seq_slot[i] >= 0 ? (cu_q[i + 1] - cu_q[i] + CB - 1) / CB : 0;
+    const int nb = (cu_q[b + 1] - cu_q[b] + CB - 1) / CB;
+    if (nb <= 0) return;
+    const int e = blockIdx.x * 256 + threadIdx.x;
+    if (e >= np) return;
+    float* st = state + ((size_t)slot * heads + h) * np + e;
+    float S = *st;
+    for (int c0 = 0; c0 < nb; c0 += 8) {            // eight blocks' sums in flight
+        float own[8], dec[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = first + c0 + j;
+            own[j] = c0 + j < nb ? work[((size_t)c * heads + h) * np + e] : 0.f;
+            dec[j] = c0 + j < nb ? block_decay[(size_t)c * heads + h] : 1.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (c0 + j < nb) {
+                work[((size_t)(first + c0 + j) * heads + h) * np + e] = S;
+                S = fmaf(dec[j], S, own[j]);
+            }
+        }
+    }
+    *st = S;
+}
+
+// (3) every block's outputs: y_t = e^(cum_t) C_t S0 + sum_{s <= t} e^(cum_t - cum_s) dt_s (C_t . B_s) x_s + D x_t.
+template <typename IT>
+__global__ void __launch_bounds__(CT)
+ssm_block_out_kernel(const float* __restrict__ u, int ld_u, int x_off, int b_off, int c_off, const IT* __restrict__ raw, int n_in,
+                     size_t in_stride, int row_stride, int dt_off, const float* __restrict__ dt_bias,
+                     const float* __restrict__ a_log, const float* __restrict__ skip, int heads, int groups, int n, int p,
+                     const int* __restrict__ seq_slot, const int* __restrict__ cu_q, int n_seqs, const float* __restrict__ work,
+                     float* __restrict__ out, int ld_out) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    float* Ct = sm;                     // [CN][CL]: C_t[n] at [n][t]
+    float* Bt = Ct + CN * CL;           // [CN][CL]: B_s[n] at [n][s]
+    float* S0 = Bt + CN * CL;           // [CN][CP]
+    float* Xs = S0 + CN * CP;           // [CB][CP]
+    float* Gt = Xs + CB * CP;           // [CB][CB]: the weight of token s in token t's result at [s][t]
+    float* dt = Gt + CB * CB;
+    float* cum = dt + CB;
+    float* la = cum + CB;
+    int t0, m, slot;
+    if (!find_tokens(blockIdx.z, seq_slot, cu_q, n_seqs, &t0, &m, &slot)) return;
+    const int h = blockIdx.y, p0 = blockIdx.x * CP, g = h / (heads / groups);
+    block_steps(raw, n_in, in_stride, row_stride, dt_off + h, t0, m, expf(a_log[h]), dt_bias[h], dt, cum, la);
+    for (int idx = threadIdx.x; idx < CB * CP; idx += CT) {
+        const int s = idx / CP, j = idx - s * CP;
+        Xs[idx] = (s < m && p0 + j < p) ? u[(size_t)(t0 + s) * ld_u + x_off + (size_t)h * p + p0 + j] : 0.f;
+    }
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    const float* start = work + (((size_t)blockIdx.z * heads + h) * n) * p;
+    float gacc[4][4] = {}, sacc[4][4] = {};
+    for (int n0 = 0; n0 < n; n0 += CN) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < CB * CN; idx += CT) {
+            const int s = idx / CN, i = idx - s * CN;         // consecutive threads read consecutive n of one token
+            const bool in = s < m && n0 + i < n;
+            const float* row = u + (size_t)(t0 + s) * ld_u + (size_t)g * n + n0 + i;
+            Ct[i * CL + s] = in ? row[c_off] : 0.f;
+            Bt[i * CL + s] = in ? row[b_off] : 0.f;
+        }
+        for (int idx = threadIdx.x; idx < CN * CP; idx += CT) {
+            const int i = idx / CP, j = idx - i * CP;
+            S0[idx] = (n0 + i < n && p0 + j < p) ? start[(size_t)(n0 + i) * p + p0 + j] : 0.f;
+        }
+        __syncthreads();
+        tile_mm(gacc, Ct, CL, Bt, CL, CN, ty, tx);           // rows t, columns s
+        tile_mm(sacc, Ct, CL, S0, CP, CN, ty, tx);           // rows t, columns p
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int t = 4 * ty + i, s = 4 * tx + j;
+            Gt[s * CB + t] = (s <= t && t < m) ? gacc[i][j] * expf(cum[t] - cum[s]) * dt[s] : 0.f;
+        }
+    __syncthreads();
+    float yacc[4][4] = {};
+    tile_mm(yacc, Gt, CB, Xs, CP, CB, ty, tx);
+    const float dskip = skip[h];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = 4 * ty + i;
+        if (t >= m) continue;
+        const float e = expf(cum[t]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int col = p0 + 4 * tx + j;
+            if (col < p) out[(size_t)(t0 + t) * ld_out + (size_t)h * p + col] = fmaf(e, sacc[i][j], yacc[i][j]) + dskip * Xs[t * CP + 4 * tx + j];
+        }
+    }
+}
+
 // What follows the recurrence: y times act(z), z columns of the projection (the gate comes first), then divided by
 // the root mean square of each of `groups` equal parts of the row (eps inside the root), times a weight vector;
 // written in the activations' type for the output product.  One block a token, the gated row in shared memory; few
@@ -305,6 +514,40 @@ extern "C" int rb_ssm_scan(const float* u, int ld_u, int x_off, int b_off, int c
     else if (raw_dtype == RB_BF16) RB_SCAN(__nv_bfloat16);
     else return RB_ERR_BAD_DTYPE;
 #undef RB_SCAN
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+extern "C" int rb_ssm_scan_blocks(const float* u, int ld_u, int x_off, int b_off, int c_off, const void* raw, int raw_dtype,
+                                  int n_in, long long in_stride, int row_stride, int dt_off, const float* dt_bias,
+                                  const float* a_log, const float* skip, int heads, int groups, int n, int p, float* state,
+                                  const int* seq_slot, const int* cu_q, int n_seqs, int n_blocks, float* work,
+                                  float* block_decay, float* out, int ld_out, void* stream) {
+    if (n_seqs <= 0 || n_blocks <= 0) return RB_OK;
+    if (heads <= 0 || groups <= 0 || heads % groups || n <= 0 || p <= 0 || n_in < 1 || n_seqs > 65535 || heads > 65535 ||
+        n_blocks > 65535)
+        return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((p + CP - 1) / CP, heads, n_blocks);
+    const size_t smem = (size_t)(2 * CN * CL + CN * CP + CB * CP + CB * CB + 3 * CB) * sizeof(float);
+#define RB_SSB(IT)                                                                                                              \
+    do {                                                                                                                        \
+        RB_LAUNCH((ssm_block_sum_kernel<IT>), grid, dim3(CT), 0, s, u, ld_u, x_off, b_off, (const IT*)raw, n_in, (size_t)in_stride, \
+                  row_stride, dt_off, dt_bias, a_log, heads, groups, n, p, seq_slot, cu_q, n_seqs, work, block_decay);           \
+        RB_LAUNCH_CHECK();                                                                                                      \
+        RB_LAUNCH((ssm_block_states_kernel), dim3((n * p + 255) / 256, heads, n_seqs), dim3(256), 0, s, work, block_decay, state, \
+                  heads, n * p, seq_slot, cu_q);                                                                                 \
+        RB_LAUNCH_CHECK();                                                                                                      \
+        auto k = ssm_block_out_kernel<IT>;                                                                                      \
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                        \
+        if (e != cudaSuccess) return (int)e;                                                                                    \
+        RB_LAUNCH((k), grid, dim3(CT), smem, s, u, ld_u, x_off, b_off, c_off, (const IT*)raw, n_in, (size_t)in_stride, row_stride, \
+                  dt_off, dt_bias, a_log, skip, heads, groups, n, p, seq_slot, cu_q, n_seqs, work, out, ld_out);                 \
+    } while (0)
+    if (raw_dtype == RB_F32) RB_SSB(float);
+    else if (raw_dtype == RB_BF16) RB_SSB(__nv_bfloat16);
+    else return RB_ERR_BAD_DTYPE;
+#undef RB_SSB
     RB_LAUNCH_CHECK();
     return RB_OK;
 }

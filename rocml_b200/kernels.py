@@ -185,6 +185,8 @@ def _lib():
         lib.rb_causal_conv.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]
         lib.rb_ssm_scan.argtypes = [_vp, _i, _i, _i, _i, _vp, _i, _i, _ll, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp,
                                     _vp, _i, _vp, _i, _vp]
+        lib.rb_ssm_scan_blocks.argtypes = [_vp, _i, _i, _i, _i, _vp, _i, _i, _ll, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp,
+                                           _vp, _i, _i, _vp, _vp, _vp, _i, _vp]
         lib.rb_gate_group_norm.argtypes = [_vp, _i, _vp, _i, _i, _ll, _i, _i, _vp, _f, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp]
         lib.rb_latent_rot_prep.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _vp,
                                            _vp, _vp, _vp, _i, _i, _vp]
@@ -1505,6 +1507,40 @@ def ssm_scan(u: torch.Tensor, n_tokens: int, x_off: int, b_off: int, c_off: int,
                             _f32vec(skip, heads, "ssm_scan: skip"), heads, groups, n, p, _ptr(state), _i32(seq_slot, "seq_slot"),
                             _i32(cu_q, "cu_q"), n_seqs, _ptr(out), out.stride(0), _stream())
     _check(rc, "ssm_scan")
+
+
+SSM_BLOCK = 64        # tokens a block of ssm_scan_blocks
+
+
+@_profiled(lambda a, facts: (a["n_tokens"] * 4 * (a["u"].shape[1] + a["heads"] * a["p"]) + 8 * a["n_seqs"] * a["heads"] * a["n"] * a["p"],
+                             a["n_tokens"] * a["heads"] * (4 * a["n"] * a["p"] + 2 * SSM_BLOCK * (a["n"] + a["p"]))))
+def ssm_scan_blocks(u: torch.Tensor, n_tokens: int, x_off: int, b_off: int, c_off: int, proj: torch.Tensor, dt_off: int,
+                    dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor, heads: int, groups: int, n: int, p: int,
+                    state: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, n_seqs: int, out: torch.Tensor,
+                    work: torch.Tensor, block_decay: torch.Tensor):
+    """``ssm_scan`` for prompts: blocks of 64 tokens run side by side (each block's own sum, the states the blocks start
+    from along every sequence, each block's outputs).  ``work``: float32 [blocks, heads, n, p], ``block_decay``: float32
+    [blocks, heads], blocks >= n_tokens // 64 + n_seqs.  The results differ from ``ssm_scan`` by rounding only."""
+    n_in, in_stride, row_stride = _partials(proj, "ssm_scan_blocks")
+    if u.dtype != torch.float32 or u.stride(-1) != 1 or max(b_off, c_off) + groups * n > u.shape[-1] or x_off + heads * p > u.shape[-1]:
+        raise KernelError("ssm_scan_blocks: u must be float32 rows that hold x, B and C")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, n, p):
+        raise KernelError("ssm_scan_blocks: state must be contiguous float32 [slots, heads, n, p]")
+    if out.dtype != torch.float32 or out.stride(-1) != 1 or out.shape[-1] != heads * p or out.shape[0] < n_tokens:
+        raise KernelError("ssm_scan_blocks: out must be float32 [T, heads * p]")
+    if dt_off + heads > proj.shape[-1] or heads % groups:
+        raise KernelError("ssm_scan_blocks: the step sizes must lie inside the projection rows, and groups divide heads")
+    blocks = work.shape[0]
+    if work.dtype != torch.float32 or not work.is_contiguous() or tuple(work.shape[1:]) != (heads, n, p) or \
+            blocks < n_tokens // SSM_BLOCK + n_seqs or block_decay.dtype != torch.float32 or not block_decay.is_contiguous() or \
+            tuple(block_decay.shape) != (blocks, heads):
+        raise KernelError("ssm_scan_blocks: work must be float32 [n_tokens // 64 + n_seqs, heads, n, p], block_decay [blocks, heads]")
+    rc = _lib().rb_ssm_scan_blocks(_ptr(u), u.stride(0), x_off, b_off, c_off, _ptr(proj), dtype_code(proj.dtype), n_in, in_stride,
+                                   row_stride, dt_off, _f32vec(dt_bias, heads, "ssm_scan_blocks: dt_bias"),
+                                   _f32vec(a_log, heads, "ssm_scan_blocks: a_log"), _f32vec(skip, heads, "ssm_scan_blocks: skip"),
+                                   heads, groups, n, p, _ptr(state), _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), n_seqs, blocks,
+                                   _ptr(work), _ptr(block_decay), _ptr(out), out.stride(0), _stream())
+    _check(rc, "ssm_scan_blocks")
 
 
 @_profiled(lambda a, facts: (a["n_tokens"] * a["y"].shape[1] * (4 + _esz(a["proj"]) * _n_in(a["proj"]) + _esz(a["out"])),

@@ -11,7 +11,8 @@
 What a sequence keeps, whatever its length: the state (``StateRequirement`` [heads, state, head_dim], 32-bit) and the
 convolution's last conv_taps - 1 inputs (a second state, [conv_taps - 1, channels]).  One stacked product makes the
 five blocks of columns from the layer's input; one kernel convolves and applies silu (32-bit out); one kernel carries the
-step's tokens through the recurrence from the state the step before left; one kernel gates and normalises; the output
+step's tokens through the recurrence from the state the step before left (single tokens and short pieces token after
+token; prompts by blocks of 64 tokens that run side by side, three kernels); one kernel gates and normalises; the output
 product is the one every mixer uses.  From the projection on everything is 32-bit: step sizes, decays, state, sums,
 the gate, the norm.
 """
@@ -29,6 +30,10 @@ from ..profile import scope
 from ..weights.decl import TensorDecl
 from .base import BuildEnv, DeferredNorm, Mixer, register_mixer
 from .linear import Linear
+
+# A step whose longest sequence brings more tokens than this runs the recurrence by blocks of 64 tokens side by side
+# (three kernels); up to it, token after token in one kernel (also every decode step).
+BLOCKS_MIN_TOKENS = 16
 
 TENSOR_NAMES = {"in": "in_proj", "conv": "conv", "dt_bias": "dt_bias", "a_log": "A_log", "skip": "D", "norm": "norm", "o": "out_proj"}
 
@@ -103,8 +108,9 @@ class StateSpace(Mixer):
     def workspace_bytes(self, n_tokens: int) -> int:
         esz = 4 if self.env.mode == "float32" else 2
         parts = 8 if n_tokens <= 128 else 1
+        blocks = (n_tokens // 64 + 8) * self.heads * (self.n * self.hd + 1) * 4 if n_tokens > BLOCKS_MIN_TOKENS else 0
         return n_tokens * (self.proj.n * max(esz, 4 * parts if parts > 1 else esz) + self.channels * 4 + self.inner * (4 + esz)
-                           + self.hidden * 4 * parts)
+                           + self.hidden * 4 * parts) + blocks
 
     def cost(self, q_lens, kv_lens):
         T = sum(q_lens)
@@ -127,8 +133,16 @@ class StateSpace(Mixer):
                                 batch.seq_slot, batch.cu_q, batch.n_seqs, batch.max_q_len, u)
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
         with scope(op="ssm_scan"):
-            kernels.ssm_scan(u, T, 0, self.inner, self.inner + gn, proj, self.dt_off, self.dt_bias, self.a_log, self.skip,
-                             self.heads, self.groups, self.n, self.hd, view.state, batch.seq_slot, batch.cu_q, batch.n_seqs, y)
+            if not batch.is_decode and batch.max_q_len > BLOCKS_MIN_TOKENS:
+                blocks = T // kernels.SSM_BLOCK + batch.n_seqs
+                work = torch.empty((blocks, self.heads, self.n, self.hd), dtype=torch.float32, device=dev)
+                decay = torch.empty((blocks, self.heads), dtype=torch.float32, device=dev)
+                kernels.ssm_scan_blocks(u, T, 0, self.inner, self.inner + gn, proj, self.dt_off, self.dt_bias, self.a_log, self.skip,
+                                        self.heads, self.groups, self.n, self.hd, view.state, batch.seq_slot, batch.cu_q,
+                                        batch.n_seqs, y, work, decay)
+            else:
+                kernels.ssm_scan(u, T, 0, self.inner, self.inner + gn, proj, self.dt_off, self.dt_bias, self.a_log, self.skip,
+                                 self.heads, self.groups, self.n, self.hd, view.state, batch.seq_slot, batch.cu_q, batch.n_seqs, y)
         g = torch.empty((T, self.inner), dtype=act, device=dev)
         with scope(op="gate_norm"):
             kernels.gate_group_norm(y, proj, self.z_off, self.norm_w, self.norm_eps, self.norm_groups, "silu", g,

@@ -129,7 +129,8 @@ def test_short_convolution_with_kept_inputs(taps, parts):
 
 @pytest.mark.parametrize("heads, groups, n, p", [(4, 2, 8, 16), (1, 1, 5, 36), (6, 6, 64, 64), (3, 1, 128, 100), (8, 2, 16, 4)])
 @pytest.mark.parametrize("parts", [1, 2])
-def test_recurrence_with_a_step_size_per_token(heads, groups, n, p, parts):
+@pytest.mark.parametrize("by_blocks", [False, True])
+def test_recurrence_with_a_step_size_per_token(heads, groups, n, p, parts, by_blocks):
     """Prompts, pieces and single tokens through the recurrence, the state carried in the slot from step to step; decays near
     one, so that the first tokens still count hundreds of tokens later (the plain result without them is far away)."""
     from rocml_b200 import kernels
@@ -170,8 +171,15 @@ def test_recurrence_with_a_step_size_per_token(heads, groups, n, p, parts):
         proj = raw.to(DEV) if parts == 1 else torch.stack([raw * 0.75, raw * 0.25]).to(DEV)
         cu = [0, lens[0], lens[0] + lens[1]]
         out = torch.zeros((u.shape[0], inner), device=DEV)
-        kernels.ssm_scan(u, u.shape[0], 0, inner, inner + gn, proj, 3, dt_bias.to(DEV), a_log.to(DEV), skip.to(DEV), heads, groups,
-                         n, p, state, i32(slots), i32(cu), 2, out)
+        if by_blocks and max(lens) > 1:       # prompts: blocks of 64 tokens side by side
+            blocks = u.shape[0] // 64 + 2
+            work = torch.full((blocks, heads, n, p), float("nan"), device=DEV)
+            decay = torch.full((blocks, heads), float("nan"), device=DEV)
+            kernels.ssm_scan_blocks(u, u.shape[0], 0, inner, inner + gn, proj, 3, dt_bias.to(DEV), a_log.to(DEV), skip.to(DEV), heads,
+                                    groups, n, p, state, i32(slots), i32(cu), 2, out, work, decay)
+        else:
+            kernels.ssm_scan(u, u.shape[0], 0, inner, inner + gn, proj, 3, dt_bias.to(DEV), a_log.to(DEV), skip.to(DEV), heads, groups,
+                             n, p, state, i32(slots), i32(cu), 2, out)
         ref = torch.cat([w[0][a:a + k] for w, a, k in zip(want, at, lens)])
         assert close(out, ref, 3e-5), lens
         at = [a + k for a, k in zip(at, lens)]

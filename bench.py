@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine at Qwen3-8B layer sizes, random bfloat16 weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
-    python bench.py --workload 4b-long | 32b | pipilix | zokelorn | safesun
+    python bench.py --workload 4b-long | 32b | pipilix | zokelorn | safesun | tibenex
 
 A step is one decode step of the default batch (8 sequences, prompts of 1,024 tokens, cache
 sized for a context of 4,096 per sequence).  One JSON line goes to stdout:
@@ -26,7 +26,8 @@ against the device's limits, and every kind of kernel's time and efficiency (``r
 ``--workload zokelorn`` does the same for the Zokelorn decoder (attention over blocks of positions, linear attention
 with a decay per head, grouped experts with a shared one, parallel layers), and ``--workload safesun`` for the Safesun
 decoder (parallel layers with two norms, windowed attention that keeps the first positions, a softmax with one more term
-in its denominator, values blended across layers).  Sweeps, timelines and kernel
+in its denominator, values blended across layers), and ``--workload tibenex`` for the Tibenex decoder (layers that
+normalise after the sum, state-space mixers, latent attention with a rotated key part, attention with mixed heads).  Sweeps, timelines and kernel
 measurements are ``python -m rocml_b200.measure``.
 
 The engine works on one GPU: for ``--gpus`` above 1 it says so and exits with 2.
@@ -53,7 +54,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the 32-bit path")
-    ap.add_argument("--workload", default=None, choices=["4b-long", "32b", "pipilix", "zokelorn", "safesun"],
+    ap.add_argument("--workload", default=None, choices=["4b-long", "32b", "pipilix", "zokelorn", "safesun", "tibenex"],
                     help="instead of the bench line: a whole generation of that workload through Engine.generate")
     args = ap.parse_args()
 
@@ -67,7 +68,7 @@ def main():
         return 2
 
     from rocml_b200 import measure as M
-    if args.workload in ("pipilix", "zokelorn", "safesun"):
+    if args.workload in ("pipilix", "zokelorn", "safesun", "tibenex"):
         print(json.dumps(M.compare(None, args.layers, steps=max(8, min(args.steps, 64)), family=args.workload)))
         return 0
     if args.workload:

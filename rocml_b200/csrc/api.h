@@ -166,14 +166,14 @@ int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void* out, int 
                              const void* v_cache, int n_pages, const int* block_table, int max_pages,
                              const int* seq_slot, const int* cu_q, const int* kv_len, int B, int max_q_len, int nq,
                              int nkv, int hd, float scale, int window, int keep, float sink, int heads_first, int* status,
-                             const void* gate, long long gate_row_stride, void* stream);
+                             const void* gate, long long gate_row_stride, int cross, void* stream);
 
 int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                         const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                         const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window, int keep, float sink,
                         int n_chunks, int pages_per_block, float* part_acc, float* part_ml, int* counters, void* out,
                         int o_stride, const void* gate, int gate_f32, int gate_n_in, long long gate_in_stride,
-                        long long gate_row_stride, void* stream);
+                        long long gate_row_stride, int cross, void* stream);
 
 int rb_attention_decode_fused(const float* proj, int n_in, long long in_stride, int row_stride, const void* q_norm_w,
                               const void* k_norm_w, int w_f32, float eps, const float* cos_sin, int write_kv,
@@ -207,9 +207,12 @@ int rb_st_read(void* handle, int i, void* dst, long long dst_bytes, int on_devic
 void rb_st_close(void* handle);
 
 // A layer whose norm follows the sum (postln.cu): resid <- rmsnorm(alpha * resid + gain * sum of the delta partial sums) * w,
-// in place, 32-bit; `out` (optional) receives the rows in the activations' type.  gain may be absent (ones).
+// in place, 32-bit; `out` (optional) receives the rows in the activations' type.  gain may be absent (ones).  next_out
+// (optional, of out_dtype; only when every row is its sequence's only one): row + (next_kept[slot] - row) * next_mu, and
+// next_kept[slot] receives the row.
 int rb_postln(float* resid, const float* delta, int n_delta, long long delta_stride, const float* gain, const float* w,
-              float alpha, float eps, void* out, int out_dtype, const int* slot_of_token, int n_rows, int H, void* stream);
+              float alpha, float eps, void* out, int out_dtype, const int* slot_of_token, int n_rows, int H,
+              const float* next_mu, float* next_kept, void* next_out, void* stream);
 // out[t] = x[t] + (x[t - 1] - x[t]) * mu, the row before a sequence's first coming from (and the last going to) kept[slot].
 int rb_token_shift(const float* x, const float* mu, float* kept, const int* seq_slot, const int* cu_q, int n_seqs,
                    int max_q_len, void* out, int out_dtype, int H, void* stream);

@@ -92,6 +92,10 @@ struct Projections {
     const float* v_first;
     const float* v_lambda;
     float* v_keep;
+    // cross (n > 1, the caches' own number of heads; not with projections): every query head's weights on the values of
+    // every stored head.  nkv = n * n then counts (key head, value head) pairs and nq = n * query heads the results; pair
+    // (a, m) sits at a * n + m, is read by the queries of key head a, and q holds nq / n heads.
+    int cross;
 };
 
 // One head of 128 values, 4 per lane: the sum of the partial sums, then (what != 2) RMSNorm with `w`
@@ -224,7 +228,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int head_chunks = (g + ROWS - 1) / ROWS;
     const int kvh = blockIdx.y / head_chunks;
     const int hc = blockIdx.y % head_chunks;
-    const int h0 = kvh * g + hc * ROWS;                     // first query head of this block
+    const int h0 = kvh * g + hc * ROWS;                     // first query head of this block (of its results, with pairs)
+    const int kh = pj.cross > 1 ? kvh / pj.cross : kvh, vh = pj.cross > 1 ? kvh % pj.cross : kvh;
+    const int n_stored = pj.cross > 1 ? pj.cross : nkv;
+    const int q_h0 = kh * g + hc * ROWS;                    // where its queries sit in q
     const int rows_valid = min(ROWS, g - hc * ROWS);
     int c = blockIdx.x, b = blockIdx.z;
     // PROP: the pages that the sequences of this head group visit, laid end to end, are cut into equal
@@ -298,11 +305,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         const bool any = page_idx <= page_last && j0 <= hi && (j0 + WK - 1 >= win_lo || j0 < keep);
         if (any) {
             const int page = table[page_idx];
-            const size_t off = (((size_t)(page < 0 ? 0 : page) * nkv + kvh) * RB_PAGE + warp * WK) * HD;
+            const size_t off = (((size_t)(page < 0 ? 0 : page) * n_stored + kh) * RB_PAGE + warp * WK) * HD;
+            const size_t off_v = (((size_t)(page < 0 ? 0 : page) * n_stored + vh) * RB_PAGE + warp * WK) * HD;
             const int valid = page < 0 ? 0 : min(WK, hi - j0 + 1);   // rows past the sequence's end are zero-filled
             __nv_bfloat16* Kw = KVw + buf * 2 * WK * HD;
             load_tile<HD>(Kw, k_cache + off, HD, WK, valid, lane, 32);
-            load_tile<HD>(Kw + WK * HD, v_cache + off, HD, WK, valid, lane, 32);
+            load_tile<HD>(Kw + WK * HD, v_cache + off_v, HD, WK, valid, lane, 32);
         }
         cp_async_commit();
     };
@@ -367,7 +375,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                                       (lane & 1) * 8) = pack4_bf16(v);
         }
     } else {
-        load_tile<HD>(Qs, q + (size_t)t * q_stride + (size_t)h0 * HD, HD, ROWS, rows_valid, threadIdx.x, WARPS * 32);
+        load_tile<HD>(Qs, q + (size_t)t * q_stride + (size_t)q_h0 * HD, HD, ROWS, rows_valid, threadIdx.x, WARPS * 32);
     }
     if (!FQ) {
         cp_async_commit();                                  // a group of its own: the wait below covers committed groups only
@@ -835,8 +843,10 @@ extern "C" int rb_attention_decode(const void* q, int q_stride, const void* k_ca
                                    const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
                                    int keep, float sink, int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
                                    int* counters, void* out, int o_stride, const void* gate, int gate_f32, int gate_n_in,
-                                   long long gate_in_stride, long long gate_row_stride, void* stream) {
+                                   long long gate_in_stride, long long gate_row_stride, int cross, void* stream) {
     Projections none = {};
+    if (cross < 0 || (cross > 1 && (nkv != cross * cross || gate != nullptr))) return RB_ERR_BAD_SIZE;
+    none.cross = cross;
     if (gate != nullptr) {      // nq * hd columns of the projection rows: the result times their sigmoid
         if (gate_n_in < 1) return RB_ERR_BAD_SIZE;
         none.gate = GateCols{gate, gate_f32, gate_n_in, gate_in_stride, gate_row_stride};
@@ -957,5 +967,5 @@ extern "C" int rb_attention_decode_static(const void* q, int q_stride, const voi
     if (e != cudaSuccess) return (int)e;
     return rb_attention_decode(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, n_seqs,
                                nq, nkv, hd, scale, window, 0, RB_NO_SINK, n_chunks, 1, sc->acc, sc->ml, sc->counters, out, o_stride,
-                               nullptr, 0, 0, 0, 0, stream);
+                               nullptr, 0, 0, 0, 0, 0, stream);
 }

@@ -116,7 +116,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slot,
                              const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
                              float scale, int window, int keep, float sink, int heads_first, int strict_order,
-                             int* __restrict__ status, const __nv_bfloat16* __restrict__ gate, long long gate_row_stride) {
+                             int* __restrict__ status, const __nv_bfloat16* __restrict__ gate, long long gate_row_stride,
+                             int cross) {
     using Z = Sizes<HD>;
     constexpr int HALVES = Z::HALVES, Q_BYTES = Z::Q_BYTES, KV_TILE = Z::KV_TILE, Q_HALF = Z::Q_HALF, KV_HALF = Z::KV_HALF;
     constexpr int TILE_BYTES = Z::TILE_BYTES, SMEM_BYTES = Z::SMEM_BYTES, TMEM_COLS = Z::TMEM_COLS;
@@ -146,7 +147,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     if (slot < 0 || m0 >= q_len) return;
     const int len = kv_len[b];
     const int pos0 = len - q_len;
+    // cross > 1: nq and nkv count (key head, value head) pairs of `cross` stored heads and their results; pair
+    // kvh = (kh, vh) is read by the queries of key head kh, and `head` numbers the results
     const int kvh = head / (nq / nkv);
+    const int kh = cross > 1 ? kvh / cross : kvh, vh = cross > 1 ? kvh % cross : kvh;
+    const int n_stored = cross > 1 ? cross : nkv;
+    const int q_head = cross > 1 ? kh * (nq / nkv) + head % (nq / nkv) : head;
     const int rows_here = min(BMQ, q_len - m0);
     const int hi = pos0 + m0 + rows_here - 1;
     const int lo = rb::span_lo(pos0 + m0, window);
@@ -187,11 +193,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             tma_prefetch_desc(&map_v);
             mbar_arrive_expect_tx(&bar->q_full, Q_BYTES);
 #pragma unroll
-            for (int h = 0; h < HALVES; ++h) tma_load_2d(Qs + h * Q_HALF, &map_q, head * HD + h * 64, q0 + m0, &bar->q_full);
+            for (int h = 0; h < HALVES; ++h) tma_load_2d(Qs + h * Q_HALF, &map_q, q_head * HD + h * 64, q0 + m0, &bar->q_full);
             bool ok = true;
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int page = table[tile_of(j)];
-                const int row = ((page < 0 ? 0 : page) * nkv + kvh) * RB_PAGE;
+                const int row = ((page < 0 ? 0 : page) * n_stored + kh) * RB_PAGE;
+                const int row_v = ((page < 0 ? 0 : page) * n_stored + vh) * RB_PAGE;
                 const int s = j & 1;
                 ok = mbar_wait(&bar->k_empty[s], ((j >> 1) & 1) ^ 1);
                 if (!ok) break;
@@ -202,7 +209,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 if (!ok) break;
                 mbar_arrive_expect_tx(&bar->v_full[s], KV_TILE);
 #pragma unroll
-                for (int h = 0; h < HALVES; ++h) tma_load_2d(Vs + s * KV_TILE + h * KV_HALF, &map_v, h * 64, row, &bar->v_full[s]);
+                for (int h = 0; h < HALVES; ++h) tma_load_2d(Vs + s * KV_TILE + h * KV_HALF, &map_v, h * 64, row_v, &bar->v_full[s]);
             }
             if (!ok) { atomicExch(status, RB_ERR_TIMEOUT); atomicExch(&bar->abort_flag, 1u); }
         }
@@ -482,13 +489,13 @@ template <int HD>
 int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, const void* k_cache, const void* v_cache,
                int n_pages, const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                const int* kv_len, int B, int max_q_len, int nq, int nkv, float scale, int window, int keep, float sink,
-               int heads_first, int* status, const void* gate, long long gate_row_stride, cudaStream_t stream) {
+               int heads_first, int* status, const void* gate, long long gate_row_stride, int cross, cudaStream_t stream) {
     // RB_PREFILL_STRICT_ORDER=0: see `strict_order` in the kernel's MMA thread
     static const int strict_order = [] { const char* e = getenv("RB_PREFILL_STRICT_ORDER"); return (e && e[0] == '0') ? 0 : 1; }();
     CUtensorMap mq, mk, mv;
     int rc;
-    if ((rc = make_map(q, T, (long long)nq * HD, q_stride, BMQ, &mq)) != RB_OK) return rc;
-    const long long cache_rows = (long long)n_pages * nkv * RB_PAGE;
+    if ((rc = make_map(q, T, (long long)(cross > 1 ? nq / cross : nq) * HD, q_stride, BMQ, &mq)) != RB_OK) return rc;
+    const long long cache_rows = (long long)n_pages * (cross > 1 ? cross : nkv) * RB_PAGE;
     if ((rc = make_map(k_cache, cache_rows, HD, HD, BNK, &mk)) != RB_OK) return rc;
     if ((rc = make_map(v_cache, cache_rows, HD, HD, BNK, &mv)) != RB_OK) return rc;
     auto k = attention_prefill_tc5_kernel<HD>;
@@ -503,7 +510,7 @@ int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, cons
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((k), grid, dim3(192), Sizes<HD>::SMEM_BYTES, stream, mq, mk, mv, (__nv_bfloat16*)out, o_stride,
               block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, keep, sink, heads_first, strict_order,
-              status, (const __nv_bfloat16*)gate, gate_row_stride);
+              status, (const __nv_bfloat16*)gate, gate_row_stride, cross);
     return RB_OK;
 }
 }  // namespace
@@ -513,13 +520,16 @@ int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, cons
 // it stay visible; sink: a score whose exponential joins every row's denominator (RB_NO_SINK: none).  Head sizes 64, 128 and 256;
 // RB_ERR_BAD_SIZE / RB_ERR_BAD_ALIGN otherwise (the caller then uses the mma.sync kernel).  gate: nq * hd bfloat16 columns of
 // the tokens' projection rows (gate_row_stride elements apart), or null: the result is multiplied by their sigmoid.
+// cross (n > 1, the caches' own number of heads): every query head's weights on the values of every stored head; nkv = n * n
+// counts (key head, value head) pairs, nq = n * query heads the results, q holds nq / n heads.
 extern "C" int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void* out, int o_stride,
                                         const void* k_cache, const void* v_cache, int n_pages,
                                         const int* block_table, int max_pages, const int* seq_slot,
                                         const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv,
                                         int hd, float scale, int window, int keep, float sink, int heads_first,
-                                        int* status, const void* gate, long long gate_row_stride, void* stream) {
+                                        int* status, const void* gate, long long gate_row_stride, int cross, void* stream) {
     if (B <= 0 || max_q_len <= 0 || T <= 0) return RB_OK;
+    if (cross < 0 || (cross > 1 && (nkv != cross * cross || gate))) return RB_ERR_BAD_SIZE;
     if (gate && (((uintptr_t)gate & 15) || (gate_row_stride % 8))) return RB_ERR_BAD_ALIGN;
     if ((hd != 64 && hd != 128 && hd != 256) || nkv <= 0 || nq % nkv || keep < 0) return RB_ERR_BAD_SIZE;
     if (window <= 0) keep = 0;                            // kept first keys stand beside a window only
@@ -527,7 +537,7 @@ extern "C" int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void
         (q_stride % 8) || (o_stride % 8))
         return RB_ERR_BAD_ALIGN;
 #define RB_TC5_ARGS q, q_stride, T, out, o_stride, k_cache, v_cache, n_pages, block_table, max_pages, seq_slot, cu_q, kv_len, \
-                    B, max_q_len, nq, nkv, scale, window, keep, sink, heads_first, status, gate, gate_row_stride, (cudaStream_t)stream
+                    B, max_q_len, nq, nkv, scale, window, keep, sink, heads_first, status, gate, gate_row_stride, cross, (cudaStream_t)stream
     if (hd == 64) return launch_tc5<64>(RB_TC5_ARGS);
     if (hd == 128) return launch_tc5<128>(RB_TC5_ARGS);
     return launch_tc5<256>(RB_TC5_ARGS);

@@ -39,13 +39,16 @@ constexpr int CONV_TOK = 32;
 constexpr int CONV_CH = 128;
 constexpr int CONV_MAX_TAPS = 16;
 
-template <typename IT>
+// TAPS > 0: the taps as a constant (the window and the taps live in registers); TAPS == 0: any number up to CONV_MAX_TAPS.
+template <typename IT, int TAPS>
 __global__ void __launch_bounds__(CONV_CH)
-causal_conv_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int col0, int channels, int taps,
+causal_conv_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int col0, int channels, int taps_arg,
                    const float* __restrict__ w, const float* __restrict__ bias, int act, float* __restrict__ kept,
                    const int* __restrict__ seq_slot, const int* __restrict__ cu_q, float* __restrict__ out, int ld_out) {
     pdl_trigger();
     pdl_wait();
+    constexpr int MAXT = TAPS > 0 ? TAPS : CONV_MAX_TAPS;
+    const int taps = TAPS > 0 ? TAPS : taps_arg;
     const int b = blockIdx.z;
     const int slot = seq_slot[b];
     if (slot < 0) return;
@@ -53,43 +56,65 @@ causal_conv_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int ro
     const int t0 = t_begin + blockIdx.y * CONV_TOK;
     if (t0 >= t_end) return;
     const int c = blockIdx.x * CONV_CH + threadIdx.x;
-    const bool live = c < channels;
+    if (c >= channels) return;
     const int back = taps - 1;
     float* mine = kept + (size_t)slot * back * channels;          // [taps - 1][channels]
-    float wt[CONV_MAX_TAPS], win[CONV_MAX_TAPS];                  // the taps, and the last inputs (win[taps-1]: the newest)
-    float bc = 0.f;
-    if (live) {
-        bc = bias ? bias[c] : 0.f;
-        for (int j = 0; j < taps; ++j) wt[j] = w[(size_t)c * taps + j];
-        for (int j = 0; j < back; ++j) {
+    float wt[MAXT], win[MAXT];                                    // the taps, and the last inputs (win[taps - 1]: the newest)
+    const float bc = bias ? bias[c] : 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXT; ++j) {
+        if (j < taps) wt[j] = w[(size_t)c * taps + j];
+        win[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < MAXT - 1; ++j) {
+        if (j < back) {
             const int t = t0 - back + j;                          // the row `back - j` before the block's first
             win[j + 1] = t >= t_begin ? sum_in(in + (size_t)t * row_stride + col0 + c, n_in, in_stride)
                                       : mine[(size_t)(back + (t - t_begin)) * channels + c];
         }
     }
     const int n = min(CONV_TOK, t_end - t0);
-    if (live) {
-        for (int tt = 0; tt < n; ++tt) {
-            for (int j = 0; j < back; ++j) win[j] = win[j + 1];
-            win[back] = sum_in(in + (size_t)(t0 + tt) * row_stride + col0 + c, n_in, in_stride);
-            float acc = bc;
-            for (int j = 0; j < taps; ++j) acc = fmaf(wt[j], win[j], acc);
-            if (act == 1) acc = silu(acc);
-            out[(size_t)(t0 + tt) * ld_out + c] = acc;
+    const IT* src = in + (size_t)t0 * row_stride + col0 + c;
+    for (int tt = 0; tt < n; tt += 4) {
+        float fresh[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) fresh[u] = tt + u < n ? sum_in(src + (size_t)(tt + u) * row_stride, n_in, in_stride) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (tt + u < n) {
+#pragma unroll
+                for (int j = 0; j < MAXT - 1; ++j)
+                    if (j < back) win[j] = win[j + 1];
+#pragma unroll
+                for (int j = 0; j < MAXT; ++j)
+                    if (j == back) win[j] = fresh[u];
+                float acc = bc;
+#pragma unroll
+                for (int j = 0; j < MAXT; ++j)
+                    if (j < taps) acc = fmaf(wt[j], win[j], acc);
+                if (act == 1) acc = silu(acc);
+                out[(size_t)(t0 + tt + u) * ld_out + c] = acc;
+            }
         }
     }
     // Only the block of a sequence's first tokens reads the slot (a block spans more tokens than there are taps), and
     // a channel's rows are read and written by one thread alone: that thread leaves the step's last inputs there.
-    if (blockIdx.y == 0 && live) {
+    if (blockIdx.y == 0 && back > 0) {
         // new rows of the slot: the last `back` inputs of (old rows, this step's rows)
         const int len = t_end - t_begin;
-        float fresh[CONV_MAX_TAPS];
-        for (int j = 0; j < back; ++j) {
-            const int src = len + j;                               // index into the concatenation of old and new rows
-            fresh[j] = src < back ? mine[(size_t)src * channels + c]
-                                  : sum_in(in + (size_t)(t_begin + src - back) * row_stride + col0 + c, n_in, in_stride);
+        float last[MAXT];
+#pragma unroll
+        for (int j = 0; j < MAXT - 1; ++j) {
+            if (j < back) {
+                const int at = len + j;                            // index into the concatenation of old and new rows
+                last[j] = at < back ? mine[(size_t)at * channels + c]
+                                    : sum_in(in + (size_t)(t_begin + at - back) * row_stride + col0 + c, n_in, in_stride);
+            }
         }
-        for (int j = 0; j < back; ++j) mine[(size_t)j * channels + c] = fresh[j];
+#pragma unroll
+        for (int j = 0; j < MAXT - 1; ++j)
+            if (j < back) mine[(size_t)j * channels + c] = last[j];
     }
 }
 
@@ -402,13 +427,54 @@ gate_group_norm_kernel(const float* __restrict__ y, int ld_y, const IT* __restri
     if (slot_of_token[t] < 0) return;
     const float* src = y + (size_t)t * ld_y;
     const IT* z = proj + (size_t)t * row_stride + z_off;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        const float g = sum_in(z + i, n_in, in_stride);
-        rowbuf[i] = src[i] * (gate_act == 1 ? silu(g) : (gate_act == 2 ? sigmoid_f32(g) : 1.f));
-    }
-    __syncthreads();
     const int gw = W / groups;
     AT* dst = out + (size_t)t * ld_out;
+    // four columns a thread where sizes and addresses allow
+    const bool vec = (gw & 3) == 0 && (ld_y & 3) == 0 && (row_stride & 3) == 0 && (z_off & 3) == 0 && (in_stride & 3) == 0 &&
+                     (ld_out & 3) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)proj & (4 * sizeof(IT) - 1)) == 0 &&
+                     ((uintptr_t)out & (4 * sizeof(AT) - 1)) == 0 && (!w || ((uintptr_t)w & 15) == 0);
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+            float v[4], g[4] = {0.f, 0.f, 0.f, 0.f};
+            load4(src + i, v);
+            for (int s = 0; s < n_in; ++s) {
+                float p[4];
+                load4(z + (size_t)s * in_stride + i, p);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) g[u] += p[u];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] *= gate_act == 1 ? silu(g[u]) : (gate_act == 2 ? sigmoid_f32(g[u]) : 1.f);
+            store4(rowbuf + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < W; i += blockDim.x) {
+            const float g = sum_in(z + i, n_in, in_stride);
+            rowbuf[i] = src[i] * (gate_act == 1 ? silu(g) : (gate_act == 2 ? sigmoid_f32(g) : 1.f));
+        }
+    }
+    __syncthreads();
+    if (vec && groups <= 8) {
+        for (int gi = 0; gi < groups; ++gi) {
+            float ss = 0.f;
+            for (int i = threadIdx.x * 4; i < gw; i += blockDim.x * 4) {
+                float v[4];
+                load4(rowbuf + gi * gw + i, v);
+                ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+            }
+            const float inv = rsqrtf(block_sum(ss, red) / (float)gw + eps);
+            for (int i = threadIdx.x * 4; i < gw; i += blockDim.x * 4) {
+                const int c = gi * gw + i;
+                float v[4], ww[4] = {1.f, 1.f, 1.f, 1.f};
+                load4(rowbuf + c, v);
+                if (w) load4(w + c, ww);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = v[u] * inv * ww[u];
+                store4(dst + c, v);
+            }
+        }
+        return;
+    }
     if (groups <= 8) {
         for (int gi = 0; gi < groups; ++gi) {
             float ss = 0.f;
@@ -471,14 +537,21 @@ extern "C" int rb_causal_conv(const void* in, int in_dtype, int n_in, long long 
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((channels + CONV_CH - 1) / CONV_CH, (max_q_len + CONV_TOK - 1) / CONV_TOK, n_seqs);
     if (grid.y > 65535) return RB_ERR_BAD_SIZE;
-    if (in_dtype == RB_F32)
-        RB_LAUNCH((causal_conv_kernel<float>), grid, dim3(CONV_CH), 0, s, (const float*)in, n_in, (size_t)in_stride, row_stride,
-                  col0, channels, taps, w, bias, act, kept, seq_slot, cu_q, out, ld_out);
-    else if (in_dtype == RB_BF16)
-        RB_LAUNCH((causal_conv_kernel<__nv_bfloat16>), grid, dim3(CONV_CH), 0, s, (const __nv_bfloat16*)in, n_in,
-                  (size_t)in_stride, row_stride, col0, channels, taps, w, bias, act, kept, seq_slot, cu_q, out, ld_out);
-    else
-        return RB_ERR_BAD_DTYPE;
+#define RB_CONV(IT, TAPS)                                                                                                      \
+    RB_LAUNCH((causal_conv_kernel<IT, TAPS>), grid, dim3(CONV_CH), 0, s, (const IT*)in, n_in, (size_t)in_stride, row_stride, col0, \
+              channels, taps, w, bias, act, kept, seq_slot, cu_q, out, ld_out)
+#define RB_CONV_T(IT)                                                                                                          \
+    do {                                                                                                                       \
+        if (taps == 4) RB_CONV(IT, 4);                                                                                         \
+        else if (taps == 3) RB_CONV(IT, 3);                                                                                    \
+        else if (taps == 2) RB_CONV(IT, 2);                                                                                    \
+        else RB_CONV(IT, 0);                                                                                                   \
+    } while (0)
+    if (in_dtype == RB_F32) RB_CONV_T(float);
+    else if (in_dtype == RB_BF16) RB_CONV_T(__nv_bfloat16);
+    else return RB_ERR_BAD_DTYPE;
+#undef RB_CONV_T
+#undef RB_CONV
     RB_LAUNCH_CHECK();
     return RB_OK;
 }

@@ -89,6 +89,41 @@ wide_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, size_t in_strid
     }
 }
 
+// The same, four neighbouring values a thread (sizes and addresses allow 4-element accesses).
+template <typename AT>
+__global__ void talk_mix4_kernel(const AT* __restrict__ o, int o_stride, const float* __restrict__ mix, AT* __restrict__ out,
+                                 int out_stride, int nq, int nkv, int hdp, int vd, const int* __restrict__ slot_of_token, int T) {
+    pdl_trigger();
+    pdl_wait();
+    const int vd4 = vd >> 2;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)T * nq * vd4) return;
+    const int d = (int)(idx % vd4) * 4;
+    const int h = (int)((idx / vd4) % nq);
+    const int t = (int)(idx / ((long long)vd4 * nq));
+    if (slot_of_token[t] < 0) return;
+    const int gs = nq / nkv, m = h / gs;
+    const AT* row = o + (size_t)t * o_stride + d;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int g0 = 0; g0 < nq; g0 += 4) {            // four heads' loads in flight
+        float x[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int g = g0 + u, a = g / gs;
+            if (g < nq) load4(row + (size_t)((a * nkv + m) * gs + (g - a * gs)) * hdp, x[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (g0 + u < nq) {
+                const float f = mix[h * nq + g0 + u];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[j] = fmaf(f, x[u][j], acc[j]);
+            }
+        }
+    }
+    store4(out + (size_t)t * out_stride + (size_t)h * vd + d, acc);
+}
+
 template <typename AT>
 __global__ void talk_mix_kernel(const AT* __restrict__ o, int o_stride, const float* __restrict__ mix, AT* __restrict__ out,
                                 int out_stride, int nq, int nkv, int hdp, int vd, const int* __restrict__ slot_of_token, int T) {
@@ -149,6 +184,20 @@ extern "C" int rb_talk_mix(const void* o, int o_stride, const float* mix, void* 
     if (T <= 0) return RB_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || vd <= 0 || hdp < vd) return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    const size_t esz = dtype == RB_BF16 ? 2 : 4;
+    if ((vd & 3) == 0 && (hdp & 3) == 0 && (o_stride & 3) == 0 && (out_stride & 3) == 0 && ((uintptr_t)o & (4 * esz - 1)) == 0 &&
+        ((uintptr_t)out & (4 * esz - 1)) == 0 && (dtype == RB_BF16 || dtype == RB_F32)) {
+        const long long blocks4 = ((long long)T * nq * (vd >> 2) + 255) / 256;
+        if (blocks4 > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
+        if (dtype == RB_BF16)
+            RB_LAUNCH((talk_mix4_kernel<__nv_bfloat16>), dim3((unsigned)blocks4), dim3(256), 0, s, (const __nv_bfloat16*)o, o_stride,
+                      mix, (__nv_bfloat16*)out, out_stride, nq, nkv, hdp, vd, slot_of_token, T);
+        else
+            RB_LAUNCH((talk_mix4_kernel<float>), dim3((unsigned)blocks4), dim3(256), 0, s, (const float*)o, o_stride, mix,
+                      (float*)out, out_stride, nq, nkv, hdp, vd, slot_of_token, T);
+        RB_LAUNCH_CHECK();
+        return RB_OK;
+    }
     const long long blocks = ((long long)T * nq * vd + 255) / 256;
     if (blocks > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
     if (dtype == RB_BF16)

@@ -208,7 +208,11 @@ class Model:
                     # (not across additions to the stream: they come before that norm)
                     nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) and not sched[i + 1].add_input \
                         and sched[i + 1].add_row is None else None
-                    pending = block.forward(resid, pending, batch, cache.views[i], next_block=nxt)
+                    if getattr(block, "wants_next_view", False):
+                        pending = block.forward(resid, pending, batch, cache.views[i], next_block=nxt,
+                                                next_view=cache.views[i + 1] if nxt is not None else None)
+                    else:
+                        pending = block.forward(resid, pending, batch, cache.views[i], next_block=nxt)
                 else:
                     pending = block.forward(resid, pending, batch, cache.views[i])
         if batch.n_want == 0:

@@ -141,9 +141,9 @@ def _lib():
         lib.rb_attention_prefill.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                              _f, _i, _i, _f, _vp]
         lib.rb_attention_prefill_tc5.argtypes = [_vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i,
-                                                 _i, _i, _i, _f, _i, _i, _f, _i, _vp, _vp, _ll, _vp]
+                                                 _i, _i, _i, _f, _i, _i, _f, _i, _vp, _vp, _ll, _i, _vp]
         lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _f, _i,
-                                            _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _ll, _ll, _vp]
+                                            _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _ll, _ll, _i, _vp]
         lib.rb_attention_decode_fused.argtypes = [_vp, _i, _ll, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _i, _ll, _f, _i,
                                                   _vp, _vp, _vp, _i, _vp, _vp,
                                                   _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp, _vp, _i,
@@ -180,7 +180,7 @@ def _lib():
                                              _i, _vp, _vp, _i, _vp]
         lib.rb_group_norm_gate.argtypes = [_vp, _i, _vp, _i, _i, _ll, _i, _i, _vp, _i, _f, _i, _i, _i, _vp, _i, _i, _vp,
                                            _i, _vp]
-        lib.rb_postln.argtypes = [_vp, _vp, _i, _ll, _vp, _vp, _f, _f, _vp, _i, _vp, _i, _i, _vp]
+        lib.rb_postln.argtypes = [_vp, _vp, _i, _ll, _vp, _vp, _f, _f, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_token_shift.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp]
         lib.rb_causal_conv.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]
         lib.rb_ssm_scan.argtypes = [_vp, _i, _i, _i, _i, _vp, _i, _i, _ll, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp,
@@ -461,8 +461,9 @@ def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_c
                           block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                           n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
                           max_kv_len: Optional[int] = None, keep: int = 0, sink: Optional[float] = None,
-                          gate: Optional[torch.Tensor] = None) -> bool:
+                          gate: Optional[torch.Tensor] = None, cross: int = 0) -> bool:
     """bfloat16 flash attention with tcgen05 (accumulators in tensor memory, TMA loads), head sizes 64, 128 and 256.
+    ``cross`` (n > 1, the cache's own number of key/value heads): as in ``attention_generic``.
     ``keep``: beside a window the keys at positions below it stay visible; ``sink``: a score whose exponential
     joins every row's denominator.  ``gate``: bfloat16 [T, nq * hd] columns of the projection rows (a view with
     unit stride along a row); the result is multiplied by their sigmoid before it is written.
@@ -475,14 +476,16 @@ def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_c
         return False
     if gate is not None and (gate.dtype != torch.bfloat16 or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != (n_tokens, nq * hd)):
         return False
-    if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
+    if tuple(k_cache.shape[1:]) != (nkv // cross if cross > 1 else nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
         raise KernelError("attention_prefill_tc5: cache must be [pages, nkv, 64, hd]")
+    if cross > 1 and gate is not None:
+        return False
     rc = _lib().rb_attention_prefill_tc5(
         _ptr(q), q.stride(0), n_tokens, _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0],
         _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"),
         _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window), int(keep), _sink(sink),
         1 if prefill_heads_first(n_seqs, nkv, hd, max_q_len if max_kv_len is None else max_kv_len, window) else 0,
-        _ptr(status_word(q.device)), _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
+        _ptr(status_word(q.device)), _ptr(gate), gate.stride(0) if gate is not None else 0, int(cross), _stream())
     if rc in (10001, 10003):
         return False
     _check(rc, "attention_prefill_tc5")
@@ -576,8 +579,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                      n_seqs: int, nq: int, nkv: int, hd: int, scale: float, window: int, n_chunks: int,
                      part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
                      pages_per_block: int = 1, keep: int = 0, sink: Optional[float] = None,
-                     gate: Optional[torch.Tensor] = None) -> bool:
-    """``keep``: the keys at positions below it stay visible beside the window (not with ``pages_per_block`` 0);
+                     gate: Optional[torch.Tensor] = None, cross: int = 0) -> bool:
+    """``cross`` (n > 1, the cache's own number of key/value heads): as in ``attention_generic``.  ``keep``: the keys at positions below it stay visible beside the window (not with ``pages_per_block`` 0);
     ``sink``: a score whose exponential joins every row's denominator.  ``gate``: [T, nq * hd] or [S, T, nq * hd]
     (partial sums, added in order) columns of the projection rows, bfloat16 or float32, unit stride along a row: the
     result is multiplied by their sigmoid before it is written.
@@ -591,8 +594,10 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
         return False
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or q.stride(-1) != 1 or out.stride(-1) != 1:
         return False
-    if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
+    if tuple(k_cache.shape[1:]) != (nkv // cross if cross > 1 else nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
         raise KernelError("attention_decode: cache must be [pages, nkv, 64, hd]")
+    if cross > 1 and gate is not None:
+        return False
     _check_parts(part_acc, part_ml, n_chunks, "attention_decode")
     g_n, g_in, g_row = 0, 0, 0
     if gate is not None:
@@ -605,7 +610,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
         _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs, nq, nkv, hd, float(scale),
         int(window), int(keep), _sink(sink), int(n_chunks), int(pages_per_block), _ptr(part_acc), _ptr(part_ml),
         _ptr(decode_counters(q.device)), _ptr(out),
-        out.stride(0), _ptr(gate), 1 if gate is not None and gate.dtype == torch.float32 else 0, g_n, g_in, g_row, _stream())
+        out.stride(0), _ptr(gate), 1 if gate is not None and gate.dtype == torch.float32 else 0, g_n, g_in, g_row, int(cross),
+        _stream())
     if rc in (10001, 10003):
         return False
     _check(rc, "attention_decode")
@@ -1418,10 +1424,14 @@ def _f32vec(t: Optional[torch.Tensor], n: int, what: str):
 @_profiled(lambda a, facts: (a["resid"].shape[1] * ((a["n_rows"] or a["resid"].shape[0]) * (8 + 4 * _n_partials(a["delta"])
                              + (_esz(a["out"]) if a["out"] is not None else 0)) + 8), 6 * (a["n_rows"] or a["resid"].shape[0]) * a["resid"].shape[1]))
 def postln(resid: torch.Tensor, delta: Optional[torch.Tensor], gain: Optional[torch.Tensor], weight: torch.Tensor, alpha: float,
-           eps: float, out: Optional[torch.Tensor], slot_of_token: Optional[torch.Tensor] = None, n_rows: Optional[int] = None):
+           eps: float, out: Optional[torch.Tensor], slot_of_token: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
+           next_mu: Optional[torch.Tensor] = None, next_kept: Optional[torch.Tensor] = None,
+           next_out: Optional[torch.Tensor] = None):
     """resid [T, H] float32 <- rmsnorm(alpha * resid + gain * sum_s delta[s]) * weight, in place; ``delta`` float32
     [S, >= T, H] partial sums (or None), ``gain`` and ``weight`` float32 [H]; ``out`` [T, H] also receives the rows in its
-    own type.  Rows whose slot is -1 are left alone."""
+    own type.  Rows whose slot is -1 are left alone.  ``next_out`` [T, H] (with ``next_mu`` float32 [H] and ``next_kept``
+    float32 [slots, H]; only in a step of one token a sequence): the new row blended with the row its sequence's slot
+    kept, row + (kept - row) * mu, as ``token_shift`` would; the slot then keeps the new row."""
     T, H = resid.shape
     n = T if n_rows is None else n_rows
     if resid.dtype != torch.float32 or not resid.is_contiguous():
@@ -1433,10 +1443,17 @@ def postln(resid: torch.Tensor, delta: Optional[torch.Tensor], gain: Optional[to
         n_delta, stride = delta.shape[0], delta.stride(0)
     if out is not None and (not out.is_contiguous() or out.shape[-1] != H or out.numel() < n * H):
         raise KernelError("postln: out must be contiguous [T, H]")
+    if next_out is not None and (next_mu is None or next_kept is None or slot_of_token is None or not next_out.is_contiguous() or
+                                 next_out.shape[-1] != H or next_out.numel() < n * H or next_kept.dtype != torch.float32 or
+                                 not next_kept.is_contiguous() or next_kept.shape[-1] != H or
+                                 (out is not None and out.dtype != next_out.dtype)):
+        raise KernelError("postln: next_out [T, H] comes with next_mu [H], next_kept float32 [slots, H] and the rows' slots")
     rc = _lib().rb_postln(_ptr(resid), _ptr(delta), n_delta, stride, _f32vec(gain, H, "postln: gain"),
                           _f32vec(weight, H, "postln: weight"), float(alpha), float(eps), _ptr(out),
-                          dtype_code(out.dtype) if out is not None else F32,
-                          None if slot_of_token is None else _i32(slot_of_token, "slot_of_token"), n, H, _stream())
+                          dtype_code(out.dtype) if out is not None else (dtype_code(next_out.dtype) if next_out is not None else F32),
+                          None if slot_of_token is None else _i32(slot_of_token, "slot_of_token"), n, H,
+                          _f32vec(next_mu, H, "postln: next_mu") if next_out is not None else None,
+                          _ptr(next_kept) if next_out is not None else None, _ptr(next_out), _stream())
     _check(rc, "postln")
 
 

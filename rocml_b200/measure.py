@@ -10,7 +10,7 @@ workloads of the same kind, and the sweeps and timelines that the notes under ``
     python -m rocml_b200.measure float32                      the 32-bit path at the benchmark's layer sizes
     python -m rocml_b200.measure profile [--dtype float32]    the per-kernel table of --profile, random weights
     python -m rocml_b200.measure host [--model NAME]          what the Python host costs a decode step
-    python -m rocml_b200.measure compare [pipilix|zokelorn|safesun|pipilix-2k|zokelorn-4k|..]   a size of that family beside the dense decoder of equal size
+    python -m rocml_b200.measure compare [pipilix|zokelorn|safesun|tibenex|pipilix-2k|zokelorn-4k|..]   a size of that family beside the dense decoder of equal size
 
 Everything is timed on the device with CUDA events after warm-up; weights are random, token ids
 seeded uniform-random (the reference's bench repeats a filler sentence for the same purpose,
@@ -551,7 +551,7 @@ def profile_table(model=None, layers=0, batch=BATCH, dtype="bfloat16", prompt=PR
 
 # ---- one architecture beside its closest relative at equal size --------------------------------------------------
 PAIRS = {"pipilix-2k": "qwen3-like-2k", "pipilix-4k": "qwen3-like-4k", "zokelorn-2k": "qwen3-like-2k", "zokelorn-4k": "qwen3-like-4k",
-         "safesun-2k": "qwen3-like-2k", "safesun-4k": "qwen3-like-4k"}
+         "safesun-2k": "qwen3-like-2k", "safesun-4k": "qwen3-like-4k", "tibenex-2k": "qwen3-like-2k", "tibenex-4k": "qwen3-like-4k"}
 
 
 def _by_op(report):
@@ -619,7 +619,7 @@ def model_point(name, layers=0, steps=32, warmup=4, profile=True, tables=None):
 
 
 def compare(names=None, layers=0, steps=32, tables_path=None, family="pipilix"):
-    """Each size of a family (pipilix, zokelorn, safesun) beside the dense decoder of equal width, heads, layer runs and
+    """Each size of a family (pipilix, zokelorn, safesun, tibenex) beside the dense decoder of equal width, heads, layer runs and
     active feed-forward width."""
     tables = [] if tables_path else None
     out = {"workload": family, "peaks": peaks(), "pairs": []}

@@ -427,8 +427,6 @@ def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, s
     Returns whether that was done: if not, the result is as without ``gate`` and the caller gates it.
     ``cross`` (n > 1, the cache's own number of key/value heads): every query head's weights are applied to the values of
     every stored head; nkv = n * n then counts (key head, value head) pairs and nq = n * query heads the results."""
-    if cross > 1:
-        return _paged_attention_pairs(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window, cross)
     if batch.is_decode:
         chunk = DECODE_CHUNK
         T = batch.n_tokens
@@ -447,46 +445,28 @@ def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, s
             ml = torch.empty((T, nq, parts, 2), dtype=torch.float32, device=q.device)
         fast = kernels.attention_decode(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                                         batch.kv_len, batch.n_seqs, nq, nkv, hd, scale,
-                                        window, n_blocks, acc, ml, ppb, keep=keep, sink=sink, gate=gate)
+                                        window, n_blocks, acc, ml, ppb, keep=keep, sink=sink, gate=gate, cross=cross)
         n_chunks = n_pages
         if fast:
             return gate is not None
         if n_chunks > 1:
             kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                                       batch.kv_len, batch.n_seqs, 1, nq, nkv, hd, scale,
-                                      window, chunk, n_chunks, acc, ml, keep=keep, sink=sink)
+                                      window, chunk, n_chunks, acc, ml, keep=keep, sink=sink, cross=cross)
             kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, nq, hd,
                                     chunk, n_chunks, window, keep=keep, sink=sink)
             return False
     tc5_gate = gate if gate is not None and gate.dim() == 2 and gate.dtype == torch.bfloat16 else None
     if kernels.attention_prefill_tc5(q, batch.n_tokens, out, k_cache, v_cache, block_table, batch.seq_slot,
                                      batch.cu_q, batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv,
-                                     hd, scale, window, max_kv_len=batch.max_kv_len, keep=keep, sink=sink, gate=tc5_gate):
+                                     hd, scale, window, max_kv_len=batch.max_kv_len, keep=keep, sink=sink, gate=tc5_gate, cross=cross):
         return tc5_gate is not None
-    if kernels.attention_prefill(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
+    if cross <= 1 and kernels.attention_prefill(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                                  batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
                                  scale, window, keep=keep, sink=sink):
         return False
     kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
                               batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
-                              scale, window, keep=keep, sink=sink)
+                              scale, window, keep=keep, sink=sink, cross=cross)
     return False
 
-
-def _paged_attention_pairs(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window, cross) -> bool:
-    """``paged_attention`` over (key head, value head) pairs: the plain kernel, which reads a pair's keys and values from
-    two stored heads; one token a sequence splits the keys in fixed chunks and merges, as always."""
-    if batch.is_decode:
-        chunk = DECODE_CHUNK
-        T = batch.n_tokens
-        n_chunks = max(1, (batch.max_kv_len + chunk - 1) // chunk)
-        if n_chunks > 1:
-            acc = torch.empty((T, nq, n_chunks, hd), dtype=torch.float32, device=q.device)
-            ml = torch.empty((T, nq, n_chunks, 2), dtype=torch.float32, device=q.device)
-            kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q, batch.kv_len,
-                                      batch.n_seqs, 1, nq, nkv, hd, scale, window, chunk, n_chunks, acc, ml, cross=cross)
-            kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, nq, hd, chunk, n_chunks, window)
-            return False
-    kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q, batch.kv_len, batch.n_seqs,
-                              batch.max_q_len, nq, nkv, hd, scale, window, cross=cross)
-    return False

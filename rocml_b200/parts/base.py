@@ -100,6 +100,16 @@ class NormedRows(DeferredNorm):
         return self.x
 
 
+@dataclass
+class ShiftedRows:
+    """What a block leaves for the block after it when it has already blended that block's input rows with the rows of
+    the tokens before (``x``, in the activations' type; the residual holds everything).  Only the block it names takes
+    it; to any other it means 'nothing pending'."""
+
+    x: torch.Tensor
+    block: object
+
+
 class Part:
     """Common face: tensors declared, tensors loaded."""
 

@@ -9,8 +9,8 @@ import torch
 from ..config.specs import LayerSpec
 from ..profile import scope
 from ..weights.decl import TensorDecl
-from .base import (BuildEnv, DeferredNorm, NormedRows, ResidualSink, RoutedRows, build_feed_forward, build_mixer, build_norm,
-                   register_arrangement)
+from .base import (BuildEnv, DeferredNorm, NormedRows, ResidualSink, RoutedRows, ShiftedRows, build_feed_forward, build_mixer,
+                   build_norm, register_arrangement)
 
 
 # From this many tokens in a step a part is offered to add into the residual itself (the products of
@@ -361,10 +361,12 @@ class PostNormBlock:
     One kernel does a sublayer's sum and norm (``kernels.postln``): it adds the result's partial sums in their order,
     applies the vector, alpha and the norm in 32-bit, writes the stream in place and, when a product reads the row
     next, the row in the activations' type as well.  One kernel blends the rows for the mixer and hands the
-    kept row over.  Nothing is left pending for the layer after it.  A layer without a feed-forward has only the
-    first half."""
+    kept row over; in a step of one token a sequence the layer's LAST sum-and-norm kernel does that for the layer after
+    it (``ShiftedRows``), whose row before is then always the one its slot kept.  Nothing else is left pending for the
+    layer after it.  A layer without a feed-forward has only the first half."""
 
-    chains = False
+    chains = True              # forward() accepts next_block
+    wants_next_view = True     # ... and next_view, the cache view of the run that follows
 
     def __init__(self, spec: LayerSpec, hidden: int, env: BuildEnv, mixer_spec=None):
         from ..config.specs import tensor_names
@@ -476,12 +478,28 @@ class PostNormBlock:
             if d is not None:
                 kernels.residual_inject(resid, d)
 
-    def forward(self, resid, pending, batch, view):
+    def _next_shift(self, batch, next_block, next_view, resid):
+        """(mu, kept rows, rows to fill) of the block that follows, when this block's last kernel can blend its input."""
+        if not (batch.is_decode and isinstance(next_block, PostNormBlock) and next_block.token_shift and next_view is not None
+                and "shift" in next_view.extras and next_block.hidden == self.hidden and next_block.env.act_dtype == self.env.act_dtype):
+            return None, None, None
+        out = torch.empty((batch.n_tokens, self.hidden), dtype=self.env.act_dtype, device=resid.device)
+        return next_block.mu, next_view.extras["shift"].state, out
+
+    def forward(self, resid, pending, batch, view, next_block=None, next_view=None):
         from .. import kernels
         T = batch.n_tokens
         act = self.env.act_dtype
+        if isinstance(pending, ShiftedRows):
+            h = pending.x if pending.block is self else None
+            pending = None
+        else:
+            h = None
         self._join(resid, pending)
-        if self.token_shift:
+        n_mu, n_kept, n_out = self._next_shift(batch, next_block, next_view, resid)
+        if h is not None and self.token_shift:
+            pass                                    # the block before has blended this block's rows
+        elif self.token_shift:
             h = torch.empty((T, self.hidden), dtype=act, device=resid.device)
             with scope(op="token_shift"):
                 kernels.token_shift(resid, self.mu, view.extras["shift"].state, batch.seq_slot, batch.cu_q, batch.n_seqs,
@@ -494,14 +512,16 @@ class PostNormBlock:
         rows = None
         if self.ff is not None and act != torch.float32:
             rows = torch.empty((T, self.hidden), dtype=act, device=resid.device)
+        last = self.ff is None
         with scope(op="mixer_post_norm"):
-            kernels.postln(resid, delta, self.mixer_gain, self._w1, self.alpha, self.mixer_norm.eps, rows, batch.slot_of_token, T)
-        if self.ff is None:
-            return None
-        delta = _as_partial_sums(self.ff.forward(rows if rows is not None else resid, batch), T)
-        with scope(op="ff_post_norm"):
-            kernels.postln(resid, delta, self.ff_gain, self._w2, self.alpha, self.ff_norm.eps, None, batch.slot_of_token, T)
-        return None
+            kernels.postln(resid, delta, self.mixer_gain, self._w1, self.alpha, self.mixer_norm.eps, rows, batch.slot_of_token, T,
+                           next_mu=n_mu if last else None, next_kept=n_kept if last else None, next_out=n_out if last else None)
+        if not last:
+            delta = _as_partial_sums(self.ff.forward(rows if rows is not None else resid, batch), T)
+            with scope(op="ff_post_norm"):
+                kernels.postln(resid, delta, self.ff_gain, self._w2, self.alpha, self.ff_norm.eps, None, batch.slot_of_token, T,
+                               next_mu=n_mu, next_kept=n_kept, next_out=n_out)
+        return ShiftedRows(n_out, next_block) if n_out is not None else None
 
 
 def _as_partial_sums(delta, n_rows: int):

@@ -95,6 +95,23 @@ def test_norm_after_the_sum(dtype, T, H, parts, alpha, gain):
     resid = x.clone().to(DEV)
     kernels.postln(resid, None, None, w.to(DEV), alpha, 2e-5, None, None, T)
     assert close(resid, P.norm(alpha * x.double(), w.double(), 2e-5), 2e-6)
+    # one token a sequence: the same kernel blends the new rows with the rows the next layer kept, and leaves the new rows there
+    if T <= 16:
+        slots = torch.randperm(T + 3)[:T].to(torch.int32)
+        slots[1] = -1
+        kept = torch.randn(T + 3, H)
+        mu = torch.rand(H)
+        resid, kept_dev = x.clone().to(DEV), kept.clone().to(DEV)
+        blended = torch.full((T, H), 7.0, dtype=DT[dtype], device=DEV)
+        kernels.postln(resid, d.to(DEV), None if g is None else g.to(DEV), w.to(DEV), alpha, 2e-5, None, slots.to(DEV), T,
+                       next_mu=mu.to(DEV), next_kept=kept_dev, next_out=blended)
+        for t in range(T):
+            if t == 1:
+                assert float(blended[t].float().min()) == 7.0 and torch.equal(kept_dev[slots[0]].cpu(), resid[0].cpu())
+                continue
+            ref = P.token_shift(want[t:t + 1], mu.double(), before=kept[slots[t]].double())
+            assert close(blended[t:t + 1], ref, 1e-2 if dtype == "bfloat16" else 2e-6)
+            assert torch.equal(kept_dev[slots[t]].cpu(), resid[t].cpu())
 
 
 @pytest.mark.parametrize("taps", [1, 2, 4, 7])
@@ -300,6 +317,9 @@ PAIR_CASES = [
     ([700, 333, 150], [1, 1, 1], 8, 4, 64),
     ([300], [300], 9, 3, 48),
     ([1100, 65], [1, 1], 4, 4, 16),
+    ([300, 70], [300, 70], 8, 2, 128),          # head sizes that the tensor-memory kernel takes
+    ([513], [200], 4, 4, 64),
+    ([900, 200, 64], [1, 1, 1], 16, 4, 128),
 ]
 
 

@@ -228,14 +228,14 @@ int rb_causal_conv(const void* in, int in_dtype, int n_in, long long in_stride, 
 int rb_ssm_scan(const float* u, int ld_u, int x_off, int b_off, int c_off, const void* raw, int raw_dtype, int n_in,
                 long long in_stride, int row_stride, int dt_off, const float* dt_bias, const float* a_log, const float* skip,
                 int heads, int groups, int n, int p, float* state, const int* seq_slot, const int* cu_q, int n_seqs,
-                float* out, int ld_out, void* stream);
+                int one_token_each, float* out, int ld_out, void* stream);
 // The same by blocks of 64 tokens side by side (prompts).  work: float32 [n_blocks][heads][n][p], block_decay: float32
-// [n_blocks][heads], n_blocks >= the sum over sequences of ceil(tokens / 64).
+// [n_blocks][heads], cb: float32 [n_blocks][groups][64][64], n_blocks >= the sum over sequences of ceil(tokens / 64).
 int rb_ssm_scan_blocks(const float* u, int ld_u, int x_off, int b_off, int c_off, const void* raw, int raw_dtype, int n_in,
                        long long in_stride, int row_stride, int dt_off, const float* dt_bias, const float* a_log,
                        const float* skip, int heads, int groups, int n, int p, float* state, const int* seq_slot,
-                       const int* cu_q, int n_seqs, int n_blocks, float* work, float* block_decay, float* out, int ld_out,
-                       void* stream);
+                       const int* cu_q, int n_seqs, int n_blocks, float* work, float* block_decay, float* cb, float* out,
+                       int ld_out, void* stream);
 // out = rmsnorm over each of `groups` parts of (y * act(z)) * w; z columns of the projection rows; act 1 silu, 2 sigmoid.
 int rb_gate_group_norm(const float* y, int ld_y, const void* proj, int proj_dtype, int n_in, long long in_stride,
                        int row_stride, int z_off, const float* w, float eps, int groups, int W, int gate_act, void* out,

@@ -18,8 +18,11 @@
 //                 block that starts from S0:
 //                   y_t   = e^(c_t) S0^T C_t + sum_{s <= t} e^(c_t - c_s) (C_t . B_s) dt_s x_s + D x_t
 //                   S_end = e^(c_m) S0 + sum_s e^(c_m - c_s) dt_s B_s x_s^T
-//                 every exponent is <= 0.  Three kernels: each block's own sum; the states the blocks start from, along
-//                 each sequence; each block's outputs.  All 32-bit FMA.
+//                 every exponent is <= 0.  Four kernels: C_t . B_s per block and group (what a group's heads share); each
+//                 block's own sum; the states the blocks start from, along each sequence; each block's outputs.  All
+//                 32-bit FMA.
+//   ssm_step      one token a sequence: the state streams through registers (a warp every eighth row, a lane a column),
+//                 read, decayed, updated and written once; nothing of it passes through shared memory.
 #include "common.cuh"
 #include "api.h"
 
@@ -201,6 +204,62 @@ ssm_scan_kernel(const float* __restrict__ u, int ld_u, int x_off, int b_off, int
         if (jj < vt) st[(size_t)i * p + jj] = S[idx];
     }
 }
+// ---- one token a sequence: the state streams through registers ---------------------------------------------------------
+template <typename IT>
+__global__ void __launch_bounds__(256)
+ssm_step_kernel(const float* __restrict__ u, int ld_u, int x_off, int b_off, int c_off, const IT* __restrict__ raw, int n_in,
+                size_t in_stride, int row_stride, int dt_off, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                const float* __restrict__ skip, int heads, int groups, int n, int p, float* __restrict__ state,
+                const int* __restrict__ seq_slot, const int* __restrict__ cu_q, float* __restrict__ out, int ld_out) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float part[8][32];
+    float* cs = sm;            // [n]  C
+    float* bs = sm + n;        // [n]  dt * B
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    const int t = cu_q[b];
+    if (cu_q[b + 1] <= t) return;
+    const int g = h / (heads / groups);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = blockIdx.x * 32 + lane;
+    const float dt = softplus_f32(sum_in(raw + (size_t)t * row_stride + dt_off + h, n_in, in_stride) + dt_bias[h]);
+    const float a = expf(-expf(a_log[h]) * dt);
+    const float* row = u + (size_t)t * ld_u;
+    for (int i = threadIdx.x; i < n; i += 256) {
+        cs[i] = row[c_off + g * n + i];
+        bs[i] = row[b_off + g * n + i] * dt;
+    }
+    const float x = j < p ? row[x_off + h * p + j] : 0.f;
+    __syncthreads();
+    float* S = state + (((size_t)slot * heads + h) * n) * p + j;
+    float acc = 0.f;
+    if (j < p) {
+        int i = warp;
+        for (; i + 24 < n; i += 32) {             // four rows' loads in flight
+            float s0 = S[(size_t)i * p], s1 = S[(size_t)(i + 8) * p], s2 = S[(size_t)(i + 16) * p], s3 = S[(size_t)(i + 24) * p];
+            s0 = fmaf(bs[i], x, a * s0); s1 = fmaf(bs[i + 8], x, a * s1); s2 = fmaf(bs[i + 16], x, a * s2); s3 = fmaf(bs[i + 24], x, a * s3);
+            S[(size_t)i * p] = s0; S[(size_t)(i + 8) * p] = s1; S[(size_t)(i + 16) * p] = s2; S[(size_t)(i + 24) * p] = s3;
+            acc = fmaf(s0, cs[i], acc); acc = fmaf(s1, cs[i + 8], acc); acc = fmaf(s2, cs[i + 16], acc); acc = fmaf(s3, cs[i + 24], acc);
+        }
+        for (; i < n; i += 8) {
+            const float s0 = fmaf(bs[i], x, a * S[(size_t)i * p]);
+            S[(size_t)i * p] = s0;
+            acc = fmaf(s0, cs[i], acc);
+        }
+    }
+    part[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && j < p) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) o += part[w][lane];
+        out[(size_t)t * ld_out + (size_t)h * p + j] = fmaf(skip[h], x, o);
+    }
+}
+
 // ---- prompts: the same recurrence by blocks of 64 tokens, all blocks at once ------------------------------------------------
 constexpr int CB = 64;              // tokens a block
 constexpr int CT = 256;             // threads: a 16 x 16 grid, each thread a 4 x 4 tile of a 64 x 64 result
@@ -277,6 +336,7 @@ ssm_block_sum_kernel(const float* __restrict__ u, int ld_u, int x_off, int b_off
     block_steps(raw, n_in, in_stride, row_stride, dt_off + h, t0, m, expf(a_log[h]), dt_bias[h], dt, cum, la);
     const float last = cum[CB - 1];
     if (threadIdx.x == 0 && blockIdx.x == 0) block_decay[(size_t)blockIdx.z * heads + h] = expf(last);
+    if (threadIdx.x < CB) la[threadIdx.x] = expf(last - cum[threadIdx.x]) * dt[threadIdx.x];     // token s's weight in the block's sum
     for (int idx = threadIdx.x; idx < CB * CP; idx += CT) {
         const int s = idx / CP, j = idx - s * CP;
         Xs[s][j] = (s < m && p0 + j < p) ? u[(size_t)(t0 + s) * ld_u + x_off + (size_t)h * p + p0 + j] : 0.f;
@@ -287,7 +347,7 @@ ssm_block_sum_kernel(const float* __restrict__ u, int ld_u, int x_off, int b_off
         __syncthreads();
         for (int idx = threadIdx.x; idx < CB * CN; idx += CT) {
             const int s = idx / CN, i = idx - s * CN;
-            Bw[s][i] = (s < m && n0 + i < n) ? u[(size_t)(t0 + s) * ld_u + b_off + (size_t)g * n + n0 + i] * expf(last - cum[s]) * dt[s] : 0.f;
+            Bw[s][i] = (s < m && n0 + i < n) ? u[(size_t)(t0 + s) * ld_u + b_off + (size_t)g * n + n0 + i] * la[s] : 0.f;
         }
         __syncthreads();
         float acc[4][4] = {};
@@ -339,20 +399,52 @@ ssm_block_states_kernel(float* __restrict__ work, const float* __restrict__ bloc
     *st = S;
 }
 
+// (0) what the heads of a group share: W[t][s] = C_t . B_s for every block of tokens and group, stored [s][t].
+__global__ void __launch_bounds__(CT)
+ssm_block_cb_kernel(const float* __restrict__ u, int ld_u, int b_off, int c_off, int groups, int n,
+                    const int* __restrict__ seq_slot, const int* __restrict__ cu_q, int n_seqs, float* __restrict__ cb) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ __align__(16) float Ct[CN * CL];
+    __shared__ __align__(16) float Bt[CN * CL];
+    int t0, m, slot;
+    if (!find_tokens(blockIdx.y, seq_slot, cu_q, n_seqs, &t0, &m, &slot)) return;
+    const int g = blockIdx.x;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float acc[4][4] = {};
+    for (int n0 = 0; n0 < n; n0 += CN) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < CB * CN; idx += CT) {
+            const int s = idx / CN, i = idx - s * CN;
+            const bool in = s < m && n0 + i < n;
+            const float* row = u + (size_t)(t0 + s) * ld_u + (size_t)g * n + n0 + i;
+            Ct[i * CL + s] = in ? row[c_off] : 0.f;
+            Bt[i * CL + s] = in ? row[b_off] : 0.f;
+        }
+        __syncthreads();
+        tile_mm(acc, Ct, CL, Bt, CL, CN, ty, tx);            // rows t, columns s
+    }
+    float* dst = cb + ((size_t)blockIdx.y * groups + g) * CB * CB;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int sidx = 4 * tx + j;
+        *reinterpret_cast<float4*>(dst + sidx * CB + 4 * ty) = make_float4(acc[0][j], acc[1][j], acc[2][j], acc[3][j]);
+    }
+}
+
 // (3) every block's outputs: y_t = e^(cum_t) C_t S0 + sum_{s <= t} e^(cum_t - cum_s) dt_s (C_t . B_s) x_s + D x_t.
 template <typename IT>
 __global__ void __launch_bounds__(CT)
-ssm_block_out_kernel(const float* __restrict__ u, int ld_u, int x_off, int b_off, int c_off, const IT* __restrict__ raw, int n_in,
+ssm_block_out_kernel(const float* __restrict__ u, int ld_u, int x_off, int c_off, const IT* __restrict__ raw, int n_in,
                      size_t in_stride, int row_stride, int dt_off, const float* __restrict__ dt_bias,
                      const float* __restrict__ a_log, const float* __restrict__ skip, int heads, int groups, int n, int p,
                      const int* __restrict__ seq_slot, const int* __restrict__ cu_q, int n_seqs, const float* __restrict__ work,
-                     float* __restrict__ out, int ld_out) {
+                     const float* __restrict__ cb, float* __restrict__ out, int ld_out) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
     float* Ct = sm;                     // [CN][CL]: C_t[n] at [n][t]
-    float* Bt = Ct + CN * CL;           // [CN][CL]: B_s[n] at [n][s]
-    float* S0 = Bt + CN * CL;           // [CN][CP]
+    float* S0 = Ct + CN * CL;           // [CN][CP]
     float* Xs = S0 + CN * CP;           // [CB][CP]
     float* Gt = Xs + CB * CP;           // [CB][CB]: the weight of token s in token t's result at [s][t]
     float* dt = Gt + CB * CB;
@@ -368,31 +460,33 @@ ssm_block_out_kernel(const float* __restrict__ u, int ld_u, int x_off, int b_off
     }
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     const float* start = work + (((size_t)blockIdx.z * heads + h) * n) * p;
-    float gacc[4][4] = {}, sacc[4][4] = {};
+    // the weight of token s in token t's result, [s][t]: what the group's heads share, times this head's decays and step sizes
+    {
+        const float* shared_w = cb + ((size_t)blockIdx.z * groups + g) * CB * CB;
+        for (int idx = threadIdx.x * 4; idx < CB * CB; idx += CT * 4) {
+            const int sidx = idx / CB, t = idx - sidx * CB;
+            const float4 w4 = *reinterpret_cast<const float4*>(shared_w + idx);
+            const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+            float o4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o4[j] = (sidx <= t + j && t + j < m) ? wv[j] * expf(cum[t + j] - cum[sidx]) * dt[sidx] : 0.f;
+            *reinterpret_cast<float4*>(Gt + idx) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+        }
+    }
+    float sacc[4][4] = {};
     for (int n0 = 0; n0 < n; n0 += CN) {
         __syncthreads();
         for (int idx = threadIdx.x; idx < CB * CN; idx += CT) {
             const int s = idx / CN, i = idx - s * CN;         // consecutive threads read consecutive n of one token
-            const bool in = s < m && n0 + i < n;
-            const float* row = u + (size_t)(t0 + s) * ld_u + (size_t)g * n + n0 + i;
-            Ct[i * CL + s] = in ? row[c_off] : 0.f;
-            Bt[i * CL + s] = in ? row[b_off] : 0.f;
+            Ct[i * CL + s] = (s < m && n0 + i < n) ? u[(size_t)(t0 + s) * ld_u + c_off + (size_t)g * n + n0 + i] : 0.f;
         }
         for (int idx = threadIdx.x; idx < CN * CP; idx += CT) {
             const int i = idx / CP, j = idx - i * CP;
             S0[idx] = (n0 + i < n && p0 + j < p) ? start[(size_t)(n0 + i) * p + p0 + j] : 0.f;
         }
         __syncthreads();
-        tile_mm(gacc, Ct, CL, Bt, CL, CN, ty, tx);           // rows t, columns s
         tile_mm(sacc, Ct, CL, S0, CP, CN, ty, tx);           // rows t, columns p
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int t = 4 * ty + i, s = 4 * tx + j;
-            Gt[s * CB + t] = (s <= t && t < m) ? gacc[i][j] * expf(cum[t] - cum[s]) * dt[s] : 0.f;
-        }
     __syncthreads();
     float yacc[4][4] = {};
     tile_mm(yacc, Gt, CB, Xs, CP, CB, ty, tx);
@@ -559,11 +653,26 @@ extern "C" int rb_causal_conv(const void* in, int in_dtype, int n_in, long long 
 extern "C" int rb_ssm_scan(const float* u, int ld_u, int x_off, int b_off, int c_off, const void* raw, int raw_dtype, int n_in,
                            long long in_stride, int row_stride, int dt_off, const float* dt_bias, const float* a_log,
                            const float* skip, int heads, int groups, int n, int p, float* state, const int* seq_slot,
-                           const int* cu_q, int n_seqs, float* out, int ld_out, void* stream) {
+                           const int* cu_q, int n_seqs, int one_token_each, float* out, int ld_out, void* stream) {
     if (n_seqs <= 0) return RB_OK;
     if (heads <= 0 || groups <= 0 || heads % groups || n <= 0 || p <= 0 || n_in < 1 || n_seqs > 65535 || heads > 65535)
         return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (one_token_each && (size_t)2 * n * sizeof(float) <= 40 * 1024) {
+        const dim3 grid1((p + 31) / 32, heads, n_seqs);
+        const size_t smem1 = (size_t)2 * n * sizeof(float);
+        if (raw_dtype == RB_F32)
+            RB_LAUNCH((ssm_step_kernel<float>), grid1, dim3(256), smem1, s, u, ld_u, x_off, b_off, c_off, (const float*)raw, n_in,
+                      (size_t)in_stride, row_stride, dt_off, dt_bias, a_log, skip, heads, groups, n, p, state, seq_slot, cu_q, out, ld_out);
+        else if (raw_dtype == RB_BF16)
+            RB_LAUNCH((ssm_step_kernel<__nv_bfloat16>), grid1, dim3(256), smem1, s, u, ld_u, x_off, b_off, c_off,
+                      (const __nv_bfloat16*)raw, n_in, (size_t)in_stride, row_stride, dt_off, dt_bias, a_log, skip, heads, groups, n, p,
+                      state, seq_slot, cu_q, out, ld_out);
+        else
+            return RB_ERR_BAD_DTYPE;
+        RB_LAUNCH_CHECK();
+        return RB_OK;
+    }
     // a tile of the state's columns: as wide as 64 KB of shared memory hold with n rows, at most 64, at most p
     int VT = p < 64 ? p : 64;
     while (VT > 1 && (size_t)n * VT * sizeof(float) > 64 * 1024) VT = (VT + 1) / 2;
@@ -595,14 +704,16 @@ extern "C" int rb_ssm_scan_blocks(const float* u, int ld_u, int x_off, int b_off
                                   int n_in, long long in_stride, int row_stride, int dt_off, const float* dt_bias,
                                   const float* a_log, const float* skip, int heads, int groups, int n, int p, float* state,
                                   const int* seq_slot, const int* cu_q, int n_seqs, int n_blocks, float* work,
-                                  float* block_decay, float* out, int ld_out, void* stream) {
+                                  float* block_decay, float* cb, float* out, int ld_out, void* stream) {
     if (n_seqs <= 0 || n_blocks <= 0) return RB_OK;
     if (heads <= 0 || groups <= 0 || heads % groups || n <= 0 || p <= 0 || n_in < 1 || n_seqs > 65535 || heads > 65535 ||
         n_blocks > 65535)
         return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((p + CP - 1) / CP, heads, n_blocks);
-    const size_t smem = (size_t)(2 * CN * CL + CN * CP + CB * CP + CB * CB + 3 * CB) * sizeof(float);
+    const size_t smem = (size_t)(CN * CL + CN * CP + CB * CP + CB * CB + 3 * CB) * sizeof(float);
+    RB_LAUNCH((ssm_block_cb_kernel), dim3(groups, n_blocks), dim3(CT), 0, s, u, ld_u, b_off, c_off, groups, n, seq_slot, cu_q, n_seqs, cb);
+    RB_LAUNCH_CHECK();
 #define RB_SSB(IT)                                                                                                              \
     do {                                                                                                                        \
         RB_LAUNCH((ssm_block_sum_kernel<IT>), grid, dim3(CT), 0, s, u, ld_u, x_off, b_off, (const IT*)raw, n_in, (size_t)in_stride, \
@@ -614,8 +725,8 @@ extern "C" int rb_ssm_scan_blocks(const float* u, int ld_u, int x_off, int b_off
         auto k = ssm_block_out_kernel<IT>;                                                                                      \
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                        \
         if (e != cudaSuccess) return (int)e;                                                                                    \
-        RB_LAUNCH((k), grid, dim3(CT), smem, s, u, ld_u, x_off, b_off, c_off, (const IT*)raw, n_in, (size_t)in_stride, row_stride, \
-                  dt_off, dt_bias, a_log, skip, heads, groups, n, p, seq_slot, cu_q, n_seqs, work, out, ld_out);                 \
+        RB_LAUNCH((k), grid, dim3(CT), smem, s, u, ld_u, x_off, c_off, (const IT*)raw, n_in, (size_t)in_stride, row_stride,       \
+                  dt_off, dt_bias, a_log, skip, heads, groups, n, p, seq_slot, cu_q, n_seqs, work, cb, out, ld_out);             \
     } while (0)
     if (raw_dtype == RB_F32) RB_SSB(float);
     else if (raw_dtype == RB_BF16) RB_SSB(__nv_bfloat16);

@@ -184,9 +184,9 @@ def _lib():
         lib.rb_token_shift.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp]
         lib.rb_causal_conv.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]
         lib.rb_ssm_scan.argtypes = [_vp, _i, _i, _i, _i, _vp, _i, _i, _ll, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp,
-                                    _vp, _i, _vp, _i, _vp]
+                                    _vp, _i, _i, _vp, _i, _vp]
         lib.rb_ssm_scan_blocks.argtypes = [_vp, _i, _i, _i, _i, _vp, _i, _i, _ll, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp,
-                                           _vp, _i, _i, _vp, _vp, _vp, _i, _vp]
+                                           _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_gate_group_norm.argtypes = [_vp, _i, _vp, _i, _i, _ll, _i, _i, _vp, _f, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp]
         lib.rb_latent_rot_prep.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _vp,
                                            _vp, _vp, _vp, _i, _i, _vp]
@@ -1505,9 +1505,11 @@ def causal_conv(proj: torch.Tensor, n_tokens: int, col0: int, channels: int, tap
                              6 * a["n_tokens"] * a["heads"] * a["n"] * a["p"]))
 def ssm_scan(u: torch.Tensor, n_tokens: int, x_off: int, b_off: int, c_off: int, proj: torch.Tensor, dt_off: int,
              dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor, heads: int, groups: int, n: int, p: int,
-             state: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, n_seqs: int, out: torch.Tensor):
+             state: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, n_seqs: int, out: torch.Tensor,
+             one_token_each: bool = False):
     """The step's tokens through S = exp(-exp(a_log[h]) dt) S + dt B x^T, y = S^T C + skip[h] x for every (sequence, head),
-    dt = softplus(raw + dt_bias[h]).  ``u`` float32 [T, >=]: x (heads * p columns from x_off), B and C (groups * n columns
+    dt = softplus(raw + dt_bias[h]).  ``one_token_each``: every sequence brings exactly one token (a decode step); the kernel
+    then streams the state through registers instead of staging it in shared memory (rounding differs, nothing else).  ``u`` float32 [T, >=]: x (heads * p columns from x_off), B and C (groups * n columns
     from b_off and c_off; head h reads group h // (heads / groups)); raw: column dt_off + h of ``proj`` ([T, N] or partial
     sums).  ``state`` float32 [slots, heads, n, p], read and written in place; ``out`` float32 [T, heads * p]."""
     n_in, in_stride, row_stride = _partials(proj, "ssm_scan")
@@ -1522,7 +1524,7 @@ def ssm_scan(u: torch.Tensor, n_tokens: int, x_off: int, b_off: int, c_off: int,
     rc = _lib().rb_ssm_scan(_ptr(u), u.stride(0), x_off, b_off, c_off, _ptr(proj), dtype_code(proj.dtype), n_in, in_stride,
                             row_stride, dt_off, _f32vec(dt_bias, heads, "ssm_scan: dt_bias"), _f32vec(a_log, heads, "ssm_scan: a_log"),
                             _f32vec(skip, heads, "ssm_scan: skip"), heads, groups, n, p, _ptr(state), _i32(seq_slot, "seq_slot"),
-                            _i32(cu_q, "cu_q"), n_seqs, _ptr(out), out.stride(0), _stream())
+                            _i32(cu_q, "cu_q"), n_seqs, 1 if one_token_each else 0, _ptr(out), out.stride(0), _stream())
     _check(rc, "ssm_scan")
 
 
@@ -1534,10 +1536,10 @@ SSM_BLOCK = 64        # tokens a block of ssm_scan_blocks
 def ssm_scan_blocks(u: torch.Tensor, n_tokens: int, x_off: int, b_off: int, c_off: int, proj: torch.Tensor, dt_off: int,
                     dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor, heads: int, groups: int, n: int, p: int,
                     state: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, n_seqs: int, out: torch.Tensor,
-                    work: torch.Tensor, block_decay: torch.Tensor):
-    """``ssm_scan`` for prompts: blocks of 64 tokens run side by side (each block's own sum, the states the blocks start
-    from along every sequence, each block's outputs).  ``work``: float32 [blocks, heads, n, p], ``block_decay``: float32
-    [blocks, heads], blocks >= n_tokens // 64 + n_seqs.  The results differ from ``ssm_scan`` by rounding only."""
+                    work: torch.Tensor, block_decay: torch.Tensor, cb: torch.Tensor):
+    """``ssm_scan`` for prompts: blocks of 64 tokens run side by side (C . B per block and group, each block's own sum, the
+    states the blocks start from along every sequence, each block's outputs).  ``work``: float32 [blocks, heads, n, p],
+    ``block_decay``: float32 [blocks, heads], ``cb``: float32 [blocks, groups, 64, 64], blocks >= n_tokens // 64 + n_seqs.  The results differ from ``ssm_scan`` by rounding only."""
     n_in, in_stride, row_stride = _partials(proj, "ssm_scan_blocks")
     if u.dtype != torch.float32 or u.stride(-1) != 1 or max(b_off, c_off) + groups * n > u.shape[-1] or x_off + heads * p > u.shape[-1]:
         raise KernelError("ssm_scan_blocks: u must be float32 rows that hold x, B and C")
@@ -1550,13 +1552,15 @@ def ssm_scan_blocks(u: torch.Tensor, n_tokens: int, x_off: int, b_off: int, c_of
     blocks = work.shape[0]
     if work.dtype != torch.float32 or not work.is_contiguous() or tuple(work.shape[1:]) != (heads, n, p) or \
             blocks < n_tokens // SSM_BLOCK + n_seqs or block_decay.dtype != torch.float32 or not block_decay.is_contiguous() or \
-            tuple(block_decay.shape) != (blocks, heads):
-        raise KernelError("ssm_scan_blocks: work must be float32 [n_tokens // 64 + n_seqs, heads, n, p], block_decay [blocks, heads]")
+            tuple(block_decay.shape) != (blocks, heads) or cb.dtype != torch.float32 or not cb.is_contiguous() or \
+            tuple(cb.shape) != (blocks, groups, SSM_BLOCK, SSM_BLOCK):
+        raise KernelError("ssm_scan_blocks: work must be float32 [n_tokens // 64 + n_seqs, heads, n, p], block_decay [blocks, heads], "
+                          "cb [blocks, groups, 64, 64]")
     rc = _lib().rb_ssm_scan_blocks(_ptr(u), u.stride(0), x_off, b_off, c_off, _ptr(proj), dtype_code(proj.dtype), n_in, in_stride,
                                    row_stride, dt_off, _f32vec(dt_bias, heads, "ssm_scan_blocks: dt_bias"),
                                    _f32vec(a_log, heads, "ssm_scan_blocks: a_log"), _f32vec(skip, heads, "ssm_scan_blocks: skip"),
                                    heads, groups, n, p, _ptr(state), _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), n_seqs, blocks,
-                                   _ptr(work), _ptr(block_decay), _ptr(out), out.stride(0), _stream())
+                                   _ptr(work), _ptr(block_decay), _ptr(cb), _ptr(out), out.stride(0), _stream())
     _check(rc, "ssm_scan_blocks")
 
 

@@ -12,7 +12,8 @@ What a sequence keeps, whatever its length: the state (``StateRequirement`` [hea
 convolution's last conv_taps - 1 inputs (a second state, [conv_taps - 1, channels]).  One stacked product makes the
 five blocks of columns from the layer's input; one kernel convolves and applies silu (32-bit out); one kernel carries the
 step's tokens through the recurrence from the state the step before left (single tokens and short pieces token after
-token; prompts by blocks of 64 tokens that run side by side, three kernels); one kernel gates and normalises; the output
+token; prompts by blocks of 64 tokens that run side by side, four kernels; one token a sequence with the state streaming
+through registers); one kernel gates and normalises; the output
 product is the one every mixer uses.  From the projection on everything is 32-bit: step sizes, decays, state, sums,
 the gate, the norm.
 """
@@ -108,7 +109,7 @@ class StateSpace(Mixer):
     def workspace_bytes(self, n_tokens: int) -> int:
         esz = 4 if self.env.mode == "float32" else 2
         parts = 8 if n_tokens <= 128 else 1
-        blocks = (n_tokens // 64 + 8) * self.heads * (self.n * self.hd + 1) * 4 if n_tokens > BLOCKS_MIN_TOKENS else 0
+        blocks = (n_tokens // 64 + 8) * (self.heads * (self.n * self.hd + 1) + self.groups * 4096) * 4 if n_tokens > BLOCKS_MIN_TOKENS else 0
         return n_tokens * (self.proj.n * max(esz, 4 * parts if parts > 1 else esz) + self.channels * 4 + self.inner * (4 + esz)
                            + self.hidden * 4 * parts) + blocks
 
@@ -137,12 +138,14 @@ class StateSpace(Mixer):
                 blocks = T // kernels.SSM_BLOCK + batch.n_seqs
                 work = torch.empty((blocks, self.heads, self.n, self.hd), dtype=torch.float32, device=dev)
                 decay = torch.empty((blocks, self.heads), dtype=torch.float32, device=dev)
+                cb = torch.empty((blocks, self.groups, kernels.SSM_BLOCK, kernels.SSM_BLOCK), dtype=torch.float32, device=dev)
                 kernels.ssm_scan_blocks(u, T, 0, self.inner, self.inner + gn, proj, self.dt_off, self.dt_bias, self.a_log, self.skip,
                                         self.heads, self.groups, self.n, self.hd, view.state, batch.seq_slot, batch.cu_q,
-                                        batch.n_seqs, y, work, decay)
+                                        batch.n_seqs, y, work, decay, cb)
             else:
                 kernels.ssm_scan(u, T, 0, self.inner, self.inner + gn, proj, self.dt_off, self.dt_bias, self.a_log, self.skip,
-                                 self.heads, self.groups, self.n, self.hd, view.state, batch.seq_slot, batch.cu_q, batch.n_seqs, y)
+                                 self.heads, self.groups, self.n, self.hd, view.state, batch.seq_slot, batch.cu_q, batch.n_seqs, y,
+                                 one_token_each=batch.is_decode)
         g = torch.empty((T, self.inner), dtype=act, device=dev)
         with scope(op="gate_norm"):
             kernels.gate_group_norm(y, proj, self.z_off, self.norm_w, self.norm_eps, self.norm_groups, "silu", g,

@@ -192,11 +192,12 @@ def test_recurrence_with_a_step_size_per_token(heads, groups, n, p, parts, by_bl
             blocks = u.shape[0] // 64 + 2
             work = torch.full((blocks, heads, n, p), float("nan"), device=DEV)
             decay = torch.full((blocks, heads), float("nan"), device=DEV)
+            cb = torch.full((blocks, groups, 64, 64), float("nan"), device=DEV)
             kernels.ssm_scan_blocks(u, u.shape[0], 0, inner, inner + gn, proj, 3, dt_bias.to(DEV), a_log.to(DEV), skip.to(DEV), heads,
-                                    groups, n, p, state, i32(slots), i32(cu), 2, out, work, decay)
-        else:
+                                    groups, n, p, state, i32(slots), i32(cu), 2, out, work, decay, cb)
+        else:         # single tokens: the state through registers when told so (by_blocks), through shared memory otherwise
             kernels.ssm_scan(u, u.shape[0], 0, inner, inner + gn, proj, 3, dt_bias.to(DEV), a_log.to(DEV), skip.to(DEV), heads, groups,
-                             n, p, state, i32(slots), i32(cu), 2, out)
+                             n, p, state, i32(slots), i32(cu), 2, out, one_token_each=by_blocks and max(lens) == 1)
         ref = torch.cat([w[0][a:a + k] for w, a, k in zip(want, at, lens)])
         assert close(out, ref, 3e-5), lens
         at = [a + k for a, k in zip(at, lens)]

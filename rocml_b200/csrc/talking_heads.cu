@@ -11,7 +11,8 @@
 //                 head turn by the step's table (neighbouring pairs, or pairs half a rotation apart); query head h is
 //                 multiplied by factor[h] (a temperature on its scores); q goes out padded to hdp a head, k and v into
 //                 the token's place in the paged cache, padded alike.  32-bit until the stores.  One block a token.
-//   talk_mix      out[t][h][:] = sum_g M[h][g] * o[t][pair (g, m(h))][:], 32-bit sums, padding dropped.
+//   talk_mix      out[t][h][:] = sum_g M[h][g] * o[t][pair (g, m(h))][:], 32-bit sums, padding dropped.  Prompts: a block a
+//                 token with the token's pair results in shared memory; few tokens: a thread four values, straight from memory.
 #include "common.cuh"
 #include "api.h"
 
@@ -49,7 +50,7 @@ wide_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, size_t in_strid
                             const int* __restrict__ block_table, int max_pages) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float buf[];            // (nq + nkv) * hd floats + 33
+    extern __shared__ __align__(16) float buf[];            // (nq + nkv) * hd floats + 33
     const int qw = nq * hd, kw = nkv * hd;
     float* kb = buf + qw;
     float* red = kb + kw;
@@ -58,13 +59,36 @@ wide_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, size_t in_strid
     if (slot < 0) return;
     const IT* row = in + (size_t)t * row_stride;
     float sq = 0.f, sk = 0.f;
-    for (int i = threadIdx.x; i < qw + kw; i += blockDim.x) {
-        const float v = sum_parts(row + i, in_stride, n_in);
-        buf[i] = v;
-        if (i < qw) sq += v * v; else sk += v * v;
+    if (((qw | kw | row_stride) & 3) == 0 && (in_stride & 3) == 0 && ((uintptr_t)in & (4 * sizeof(IT) - 1)) == 0) {
+        for (int i = threadIdx.x * 4; i < qw + kw; i += blockDim.x * 4) {      // four values a load; a group of four lies in q or in k
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int s = 0; s < n_in; ++s) {
+                float p[4];
+                load4(row + (size_t)s * in_stride + i, p);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] += p[u];
+            }
+            store4(buf + i, v);
+            const float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+            if (i < qw) sq += ss; else sk += ss;
+        }
+    } else {
+        for (int i = threadIdx.x; i < qw + kw; i += blockDim.x) {
+            const float v = sum_parts(row + i, in_stride, n_in);
+            buf[i] = v;
+            if (i < qw) sq += v * v; else sk += v * v;
+        }
     }
-    const float inv_q = wq ? rsqrtf(block_sum(sq, red) / (float)qw + eps) : 1.f;
-    const float inv_k = wk ? rsqrtf(block_sum(sk, red) / (float)kw + eps) : 1.f;
+    // both sums of squares in one pass over the block
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = sq; red[8 + (threadIdx.x >> 5)] = sk; }
+    __syncthreads();
+    sq = sk = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { sq += red[w]; sk += red[8 + w]; }       // 256 threads: eight warps, added in their order
+    const float inv_q = wq ? rsqrtf(sq / (float)qw + eps) : 1.f;
+    const float inv_k = wk ? rsqrtf(sk / (float)kw + eps) : 1.f;
     for (int i = threadIdx.x; i < qw + kw; i += blockDim.x) {
         if (i < qw) { if (wq) buf[i] *= inv_q * wq[i]; }
         else if (wk) buf[i] *= inv_k * wk[i - qw];
@@ -86,6 +110,45 @@ wide_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, size_t in_strid
         const size_t at = (((size_t)page * nkv + h) * RB_PAGE + (pos % RB_PAGE)) * hdp + d;
         k_cache[at] = from_f32<AT>(d < hd ? turned(kb + h * hd, d, r, neighbours != 0, cs) : 0.f);
         v_cache[at] = from_f32<AT>(d < vd ? sum_parts(row + qw + kw + h * vd + d, in_stride, n_in) : 0.f);
+    }
+}
+
+// The same, a block a token: the token's pair results are read once into shared memory (every one of them is needed by
+// all the heads of its key/value group), then every thread forms four neighbouring values of a result head.
+template <typename AT>
+__global__ void __launch_bounds__(256)
+talk_mix_row_kernel(const AT* __restrict__ o, int o_stride, const float* __restrict__ mix, AT* __restrict__ out, int out_stride,
+                    int nq, int nkv, int hdp, int vd, const int* __restrict__ slot_of_token) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) uint8_t raw_sm[];
+    AT* row = reinterpret_cast<AT*>(raw_sm);                              // [nq * nkv][hdp]
+    float* m_s = reinterpret_cast<float*>(raw_sm + (((size_t)nq * nkv * hdp * sizeof(AT) + 15) & ~(size_t)15));   // [nq][nq]
+    const int t = blockIdx.x;
+    if (slot_of_token[t] < 0) return;
+    const int width = nq * nkv * hdp;
+    const AT* src = o + (size_t)t * o_stride;
+    for (int i = threadIdx.x * 4; i < width; i += 256 * 4) {
+        float x[4];
+        load4(src + i, x);
+        store4(row + i, x);
+    }
+    for (int i = threadIdx.x; i < nq * nq; i += 256) m_s[i] = mix[i];
+    __syncthreads();
+    const int gs = nq / nkv, vd4 = vd >> 2;
+    for (int idx = threadIdx.x; idx < nq * vd4; idx += 256) {
+        const int h = idx / vd4, d = (idx - h * vd4) * 4;
+        const int m = h / gs;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int g = 0; g < nq; ++g) {
+            const int a = g / gs;
+            float x[4];
+            load4(row + (size_t)((a * nkv + m) * gs + (g - a * gs)) * hdp + d, x);
+            const float f = m_s[h * nq + g];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = fmaf(f, x[j], acc[j]);
+        }
+        store4(out + (size_t)t * out_stride + (size_t)h * vd + d, acc);
     }
 }
 
@@ -187,6 +250,29 @@ extern "C" int rb_talk_mix(const void* o, int o_stride, const float* mix, void* 
     const size_t esz = dtype == RB_BF16 ? 2 : 4;
     if ((vd & 3) == 0 && (hdp & 3) == 0 && (o_stride & 3) == 0 && (out_stride & 3) == 0 && ((uintptr_t)o & (4 * esz - 1)) == 0 &&
         ((uintptr_t)out & (4 * esz - 1)) == 0 && (dtype == RB_BF16 || dtype == RB_F32)) {
+        // a block a token while the token's pair results fit shared memory
+        const size_t row_bytes = (((size_t)nq * nkv * hdp * esz + 15) & ~(size_t)15) + (size_t)nq * nq * sizeof(float);
+        if (row_bytes <= 160 * 1024 && T >= 64) {
+            if (dtype == RB_BF16) {
+                auto k = talk_mix_row_kernel<__nv_bfloat16>;
+                if (row_bytes > 48 * 1024) {
+                    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
+                    if (e != cudaSuccess) return (int)e;
+                }
+                RB_LAUNCH((k), dim3(T), dim3(256), row_bytes, s, (const __nv_bfloat16*)o, o_stride, mix, (__nv_bfloat16*)out, out_stride,
+                          nq, nkv, hdp, vd, slot_of_token);
+            } else {
+                auto k = talk_mix_row_kernel<float>;
+                if (row_bytes > 48 * 1024) {
+                    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
+                    if (e != cudaSuccess) return (int)e;
+                }
+                RB_LAUNCH((k), dim3(T), dim3(256), row_bytes, s, (const float*)o, o_stride, mix, (float*)out, out_stride, nq, nkv, hdp,
+                          vd, slot_of_token);
+            }
+            RB_LAUNCH_CHECK();
+            return RB_OK;
+        }
         const long long blocks4 = ((long long)T * nq * (vd >> 2) + 255) / 256;
         if (blocks4 > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
         if (dtype == RB_BF16)

@@ -446,8 +446,8 @@ ssm_block_out_kernel(const float* __restrict__ u, int ld_u, int x_off, int c_off
     float* Ct = sm;                     // [CN][CL]: C_t[n] at [n][t]
     float* S0 = Ct + CN * CL;           // [CN][CP]
     float* Xs = S0 + CN * CP;           // [CB][CP]
-    float* Gt = Xs + CB * CP;           // [CB][CB]: the weight of token s in token t's result at [s][t]
-    float* dt = Gt + CB * CB;
+    float* Gt = Ct;                     // [CB][CB]: the weight of token s in token t's result at [s][t], after the C tiles
+    float* dt = Xs + CB * CP;
     float* cum = dt + CB;
     float* la = cum + CB;
     int t0, m, slot;
@@ -460,19 +460,6 @@ ssm_block_out_kernel(const float* __restrict__ u, int ld_u, int x_off, int c_off
     }
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     const float* start = work + (((size_t)blockIdx.z * heads + h) * n) * p;
-    // the weight of token s in token t's result, [s][t]: what the group's heads share, times this head's decays and step sizes
-    {
-        const float* shared_w = cb + ((size_t)blockIdx.z * groups + g) * CB * CB;
-        for (int idx = threadIdx.x * 4; idx < CB * CB; idx += CT * 4) {
-            const int sidx = idx / CB, t = idx - sidx * CB;
-            const float4 w4 = *reinterpret_cast<const float4*>(shared_w + idx);
-            const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
-            float o4[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) o4[j] = (sidx <= t + j && t + j < m) ? wv[j] * expf(cum[t + j] - cum[sidx]) * dt[sidx] : 0.f;
-            *reinterpret_cast<float4*>(Gt + idx) = make_float4(o4[0], o4[1], o4[2], o4[3]);
-        }
-    }
     float sacc[4][4] = {};
     for (int n0 = 0; n0 < n; n0 += CN) {
         __syncthreads();
@@ -486,6 +473,20 @@ ssm_block_out_kernel(const float* __restrict__ u, int ld_u, int x_off, int c_off
         }
         __syncthreads();
         tile_mm(sacc, Ct, CL, S0, CP, CN, ty, tx);           // rows t, columns p
+    }
+    __syncthreads();                    // the C tile is done with: the weights take its room
+    // the weight of token s in token t's result, [s][t]: what the group's heads share, times this head's decays and step sizes
+    {
+        const float* shared_w = cb + ((size_t)blockIdx.z * groups + g) * CB * CB;
+        for (int idx = threadIdx.x * 4; idx < CB * CB; idx += CT * 4) {
+            const int sidx = idx / CB, t = idx - sidx * CB;
+            const float4 w4 = *reinterpret_cast<const float4*>(shared_w + idx);
+            const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+            float o4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o4[j] = (sidx <= t + j && t + j < m) ? wv[j] * expf(cum[t + j] - cum[sidx]) * dt[sidx] : 0.f;
+            *reinterpret_cast<float4*>(Gt + idx) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+        }
     }
     __syncthreads();
     float yacc[4][4] = {};
@@ -711,7 +712,7 @@ extern "C" int rb_ssm_scan_blocks(const float* u, int ld_u, int x_off, int b_off
         return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((p + CP - 1) / CP, heads, n_blocks);
-    const size_t smem = (size_t)(CN * CL + CN * CP + CB * CP + CB * CB + 3 * CB) * sizeof(float);
+    const size_t smem = (size_t)(CN * CL + CN * CP + CB * CP + 3 * CB) * sizeof(float);
     RB_LAUNCH((ssm_block_cb_kernel), dim3(groups, n_blocks), dim3(CT), 0, s, u, ld_u, b_off, c_off, groups, n, seq_slot, cu_q, n_seqs, cb);
     RB_LAUNCH_CHECK();
 #define RB_SSB(IT)                                                                                                              \
